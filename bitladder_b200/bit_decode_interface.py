@@ -1,0 +1,328 @@
+"""Python entry points of the low-bit KV-cache decode-attention path.
+
+Drop-in for the two functions of the reference's ``bit_decode`` package
+(reference: ``bit_decode/bit_decode_interface.py:10-41`` ``kvcache_pack_int`` and
+``:43-86`` ``fwd_kvcache_int``): same names, same positional arguments, same
+caller-allocated buffers with the same shapes and dtypes.  Tensors cross a C-ABI
+(``include/bitdecode.h``) as raw device pointers; the kernels are hand-written
+CUDA for sm_100a.  There is no CPU or PyTorch fallback: without the built
+library, or on a non-CUDA tensor, the calls raise ``RuntimeError``.
+
+Differences from the reference, all of them additions or stricter checks:
+
+* keyword-only extensions on the decode call: an unquantized fp16/bf16 tail
+  (``k_res``/``v_res``/``res_lens``), per-sequence lengths (``cache_seqlens``),
+  a returned log-sum-exp, a caller-provided output / workspace, fp32 output;
+* bf16 inputs and group size 64 are implemented (the reference accepts the
+  arguments but has no kernels for them);
+* unsupported ``(quant_mode, group_size, num_bits, dtype)`` combinations raise
+  instead of silently doing nothing (reference: ``csrc/bit_decode/decode_api.cpp:207-226``);
+* paged caches (``opt_block_table``) are not implemented and raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+__all__ = ["kvcache_pack_int", "fwd_kvcache_int", "combine_partials", "decode_workspace_bytes",
+           "plan_splits", "pack_block_tokens", "alloc_packed_cache"]
+
+_WORKSPACES = {}
+
+
+def pack_block_tokens(num_bits: int) -> int:
+    """Tokens per pack block: K codes are grouped 32 rows x (16 // num_bits) fields."""
+    return 32 * (16 // num_bits)
+
+
+def _dtype_code(t: torch.dtype) -> int:
+    if t == torch.float16:
+        return _lib.BD_FP16
+    if t == torch.bfloat16:
+        return _lib.BD_BF16
+    if t == torch.float32:
+        return _lib.BD_FP32
+    raise RuntimeError(f"unsupported dtype {t}: only fp16 and bf16 inputs are supported")
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _check_cuda(*tensors) -> None:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        _require(t.is_cuda, "all tensors must be on a CUDA device (there is no CPU path)")
+        dev = dev if dev is not None else t.device
+        _require(t.device == dev, "all tensors must be on the same device")
+
+
+def _check_config(quant_mode: str, group_size: int, num_bits: int) -> None:
+    _require(quant_mode == "k-channel", f"quant_mode {quant_mode!r} is not supported (only 'k-channel')")
+    _require(num_bits in (2, 4), f"num_bits must be 2 or 4, got {num_bits}")
+    _require(group_size in (64, 128), f"group_size must be 64 or 128, got {group_size}")
+
+
+def _rows_contiguous(t: torch.Tensor) -> bool:
+    """True when dims 1.. are laid out densely (dim 0 may have any stride)."""
+    expected = 1
+    for size, stride in zip(reversed(t.shape[1:]), reversed(t.stride()[1:])):
+        if size != 1 and stride != expected:
+            return False
+        expected *= size
+    return True
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def alloc_packed_cache(batch: int, seqlen: int, nheads_k: int, d: int = 128, num_bits: int = 4,
+                       group_size: int = 128, device="cuda"):
+    """Allocate the four packed buffers with the shapes the reference's callers use
+    (reference: ``evaluation/test.py:76-83``).  ``seqlen`` is rounded up to whole pack blocks."""
+    nb = pack_block_tokens(num_bits)
+    s = (seqlen + nb - 1) // nb * nb
+    pn = 16 // num_bits
+    k_pack = torch.zeros((batch, s // pn, nheads_k, d), dtype=torch.uint16, device=device)
+    k_params = torch.zeros((batch, s // group_size, nheads_k, d), dtype=torch.float32, device=device)
+    v_pack = torch.zeros((batch, s, nheads_k, d // pn), dtype=torch.uint16, device=device)
+    v_params = torch.zeros((batch, d // group_size, nheads_k, s), dtype=torch.float32, device=device)
+    return k_pack, k_params, v_pack, v_params
+
+
+def _check_packed(k_pack, k_params, v_pack, v_params, num_bits, group_size):
+    pn = 16 // num_bits
+    nb = pack_block_tokens(num_bits)
+    for name, t in (("k_pack", k_pack), ("v_pack", v_pack)):
+        _require(t.dtype in (torch.uint16, torch.int16), f"{name} must be uint16")
+    for name, t in (("k_params", k_params), ("v_params", v_params)):
+        _require(t.dtype == torch.float32, f"{name} must be float32 storage (one fp16 scale + one fp16 zero per slot)")
+    for name, t in (("k_pack", k_pack), ("k_params", k_params), ("v_pack", v_pack), ("v_params", v_params)):
+        _require(t.dim() == 4, f"{name} must have 4 dimensions")
+        _require(_rows_contiguous(t), f"{name} must be contiguous in its last three dimensions")
+    b, s_cap, h_k, dp = v_pack.shape
+    d = dp * pn
+    _require(d == 128, f"head dimension must be 128, got {d}")
+    _require(s_cap % nb == 0, f"packed sequence capacity {s_cap} must be a multiple of {nb}")
+    _require(tuple(k_pack.shape) == (b, s_cap // pn, h_k, d), "k_pack shape must be (b, s/pack_num, h_k, d)")
+    _require(tuple(k_params.shape) == (b, s_cap // group_size, h_k, d), "k_params shape must be (b, s/group, h_k, d)")
+    _require(tuple(v_params.shape) == (b, d // group_size, h_k, s_cap), "v_params shape must be (b, d/group, h_k, s)")
+    return b, s_cap, h_k, d
+
+
+def kvcache_pack_int(k_cache: torch.Tensor, k_pack: torch.Tensor, k_params: torch.Tensor,
+                     v_cache: torch.Tensor, v_pack: torch.Tensor, v_params: torch.Tensor,
+                     opt_block_table: Optional[torch.Tensor] = None,
+                     cu_seqlens_k: torch.Tensor = None,
+                     seqlen_k: int = 0,
+                     quant_mode: str = "k-channel",
+                     group_size: int = 128,
+                     num_bits: int = 4,
+                     *, dst_token_offset: int = 0) -> None:
+    """Quantize ``k_cache``/``v_cache`` (b, s, h_k, d) and pack them in place into
+    ``k_pack``/``k_params``/``v_pack``/``v_params``.
+
+    Same signature as the reference (``bit_decode_interface.py:10-41``); like
+    there, ``seqlen_k`` is taken from ``k_cache.shape[1]`` and ``cu_seqlens_k`` is
+    accepted but not read.  ``dst_token_offset`` (extension) writes the packed
+    tokens at that offset of the pack buffers, for caches that grow block by block.
+    Asynchronous on the current stream.
+    """
+    _check_config(quant_mode, group_size, num_bits)
+    _require(opt_block_table is None, "paged KV caches (opt_block_table) are not supported")
+    _check_cuda(k_cache, v_cache, k_pack, k_params, v_pack, v_params)
+    _require(k_cache.dtype in (torch.float16, torch.bfloat16), "k_cache must be fp16 or bf16")
+    _require(v_cache.dtype == k_cache.dtype, "k_cache and v_cache must have the same dtype")
+    _require(k_cache.dim() == 4 and k_cache.shape == v_cache.shape, "k_cache and v_cache must both be (b, s, h_k, d)")
+    _require(k_cache.stride(-1) == 1 and v_cache.stride(-1) == 1, "Input tensor must have contiguous last dimension")
+    b, s, h_k, d = k_cache.shape
+    pb, s_cap, ph, pd = _check_packed(k_pack, k_params, v_pack, v_params, num_bits, group_size)
+    _require((pb, ph, pd) == (b, h_k, d), "packed buffers do not match k_cache's batch / heads / head_dim")
+    nb = pack_block_tokens(num_bits)
+    _require(s % nb == 0, f"sequence length {s} must be a multiple of {nb} for {num_bits}-bit packing")
+    _require(dst_token_offset % nb == 0 and dst_token_offset >= 0, f"dst_token_offset must be a multiple of {nb}")
+    _require(dst_token_offset + s <= s_cap, "packed buffers are too small for this many tokens")
+    if s == 0:
+        return
+    a = _lib.PackArgs(
+        k=k_cache.data_ptr(), v=v_cache.data_ptr(),
+        k_stride_b=k_cache.stride(0), k_stride_s=k_cache.stride(1), k_stride_h=k_cache.stride(2),
+        v_stride_b=v_cache.stride(0), v_stride_s=v_cache.stride(1), v_stride_h=v_cache.stride(2),
+        k_pack=k_pack.data_ptr(), k_params=k_params.data_ptr(),
+        v_pack=v_pack.data_ptr(), v_params=v_params.data_ptr(),
+        k_pack_stride_b=k_pack.stride(0), k_params_stride_b=k_params.stride(0),
+        v_pack_stride_b=v_pack.stride(0),
+        v_params_stride_b=v_params.stride(0), v_params_stride_g=v_params.stride(1),
+        v_params_stride_h=v_params.stride(2),
+        b=b, s=s, h_k=h_k, d=d, dst_token_offset=dst_token_offset,
+        bits=num_bits, group=group_size, dtype=_dtype_code(k_cache.dtype))
+    with torch.cuda.device(k_cache.device):
+        _lib.check(_lib.load().bd_pack(C.byref(a), _stream(k_cache.device)), "bd_pack")
+
+
+def _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
+                 k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, lse, num_splits):
+    b, s_cap, h_k, d = _check_packed(k_pack, k_params, v_pack, v_params, num_bits, group_size)
+    _require(q.dim() == 4 and q.shape[1] == 1, "q must be (b, 1, h, d): one query token per sequence")
+    _require(q.shape[0] == b and q.shape[3] == d, "q does not match the packed cache's batch / head_dim")
+    h = q.shape[2]
+    _require(h % h_k == 0, "Number of heads in key/value must divide number of heads in query")
+    _require(h // h_k <= 16, "at most 16 query heads per KV head are supported")
+    _require(q.stride(-1) == 1, "Input tensor must have contiguous last dimension")
+    s = s_cap if seqlen_k is None else int(seqlen_k)
+    _require(0 <= s <= s_cap, "seqlen_k exceeds the packed buffers")
+    a = _lib.DecodeArgs()
+    a.q, a.out, a.lse = q.data_ptr(), out.data_ptr(), (lse.data_ptr() if lse is not None else None)
+    a.q_stride_b, a.q_stride_h = q.stride(0), q.stride(2)
+    a.out_stride_b, a.out_stride_h = out.stride(0), out.stride(2)
+    a.k_pack, a.k_params, a.v_pack, a.v_params = (k_pack.data_ptr(), k_params.data_ptr(),
+                                                  v_pack.data_ptr(), v_params.data_ptr())
+    a.k_pack_stride_b, a.k_params_stride_b, a.v_pack_stride_b = k_pack.stride(0), k_params.stride(0), v_pack.stride(0)
+    a.v_params_stride_b, a.v_params_stride_g, a.v_params_stride_h = (v_params.stride(0), v_params.stride(1),
+                                                                     v_params.stride(2))
+    if cache_seqlens is not None:
+        _require(cache_seqlens.dtype == torch.int32 and cache_seqlens.numel() == b and cache_seqlens.is_contiguous(),
+                 "cache_seqlens must be a contiguous int32 tensor of shape (b,)")
+        a.cache_seqlens = cache_seqlens.data_ptr()
+    if k_res is not None or v_res is not None:
+        _require(k_res is not None and v_res is not None, "k_res and v_res must be given together")
+        _require(k_res.dtype == q.dtype and v_res.dtype == q.dtype, "the tail must have q's dtype")
+        _require(k_res.dim() == 4 and k_res.shape == v_res.shape and k_res.stride() == v_res.stride(),
+                 "k_res and v_res must both be (b, r, h_k, d) with equal strides")
+        _require(k_res.shape[0] == b and k_res.shape[2] == h_k and k_res.shape[3] == d,
+                 "the tail does not match the packed cache's batch / heads / head_dim")
+        _require(k_res.shape[1] <= 256, "the unquantized tail holds at most 256 tokens")
+        _require(k_res.stride(-1) == 1, "Input tensor must have contiguous last dimension")
+        a.k_res, a.v_res = k_res.data_ptr(), v_res.data_ptr()
+        a.res_stride_b, a.res_stride_s, a.res_stride_h = k_res.stride(0), k_res.stride(1), k_res.stride(2)
+        a.res_len = k_res.shape[1]
+        if res_lens is not None:
+            _require(res_lens.dtype == torch.int32 and res_lens.numel() == b and res_lens.is_contiguous(),
+                     "res_lens must be a contiguous int32 tensor of shape (b,)")
+            a.res_lens = res_lens.data_ptr()
+    a.b, a.h, a.h_k, a.d = b, h, h_k, d
+    a.s, a.s_cap = s, s_cap
+    a.bits, a.group = num_bits, group_size
+    a.dtype, a.out_dtype = _dtype_code(q.dtype), _dtype_code(out.dtype)
+    a.softmax_scale = float(softmax_scale)
+    a.num_splits = int(num_splits)
+    return a
+
+
+def _workspace_for(a: "_lib.DecodeArgs", device, workspace):
+    need = int(_lib.load().bd_decode_workspace_bytes(C.byref(a)))
+    _require(need > 0, "bd_decode_workspace_bytes rejected the arguments")
+    if workspace is None:
+        key = (device.index, _stream(device))
+        workspace = _WORKSPACES.get(key)
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=device)
+            _WORKSPACES[key] = workspace
+    else:
+        _require(workspace.is_cuda and workspace.dtype == torch.uint8 and workspace.is_contiguous(),
+                 "workspace must be a contiguous uint8 CUDA tensor")
+        _require(workspace.numel() >= need, f"workspace too small: need {need} bytes")
+    a.workspace = workspace.data_ptr()
+    a.workspace_bytes = workspace.numel()
+    return workspace
+
+
+def fwd_kvcache_int(q: torch.Tensor,
+                    k_pack: torch.Tensor, k_params: torch.Tensor,
+                    v_pack: torch.Tensor, v_params: torch.Tensor,
+                    opt_block_table: Optional[torch.Tensor] = None,
+                    softmax_scale: float = 1.0,
+                    quant_mode: str = "k-channel",
+                    group_size: int = 128,
+                    num_bits: int = 4,
+                    *, k_res: Optional[torch.Tensor] = None, v_res: Optional[torch.Tensor] = None,
+                    res_lens: Optional[torch.Tensor] = None, cache_seqlens: Optional[torch.Tensor] = None,
+                    seqlen_k: Optional[int] = None, return_lse: bool = False,
+                    out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+                    workspace: Optional[torch.Tensor] = None, num_splits: int = 0):
+    """One decode-attention step over the packed cache; returns ``out`` (b, 1, h, d).
+
+    Same positional signature as the reference (``bit_decode_interface.py:43-86``),
+    which hard-wires non-causal, no window, no softcap and automatic splits; so does
+    this one.  Keyword-only extensions: ``k_res``/``v_res`` (b, r<=256, h_k, d)
+    unquantized tail attended jointly with the packed tokens (``res_lens`` int32 (b,)
+    gives per-sequence tail lengths); ``cache_seqlens`` int32 (b,) per-sequence count
+    of packed tokens; ``seqlen_k`` upper bound on packed tokens (default: the
+    buffers' capacity, like the reference's ``v_pack.size(1)``); ``return_lse``
+    also returns the (b, h) fp32 log-sum-exp of the scaled scores; ``out`` /
+    ``out_dtype`` (fp16, bf16 or fp32) / ``workspace`` / ``num_splits`` for callers
+    that manage memory and scheduling themselves.  Asynchronous on the current stream.
+    """
+    _check_config(quant_mode, group_size, num_bits)
+    _require(opt_block_table is None, "paged KV caches (opt_block_table) are not supported")
+    _check_cuda(q, k_pack, k_params, v_pack, v_params, k_res, v_res, res_lens, cache_seqlens, out, workspace)
+    _require(q.dtype in (torch.float16, torch.bfloat16), "q must be fp16 or bf16")
+    if out is None:
+        out = torch.empty(q.shape, dtype=out_dtype or q.dtype, device=q.device)
+    else:
+        _require(out.shape == q.shape and out.stride(-1) == 1, "out must have q's shape and a contiguous last dimension")
+    lse = torch.empty((q.shape[0], q.shape[2]), dtype=torch.float32, device=q.device) if return_lse else None
+    a = _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
+                     k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, lse, num_splits)
+    with torch.cuda.device(q.device):
+        ws = _workspace_for(a, q.device, workspace)
+        _lib.check(_lib.load().bd_decode(C.byref(a), _stream(q.device)), "bd_decode")
+    del ws
+    return (out, lse) if return_lse else out
+
+
+def decode_workspace_bytes(q, k_pack, k_params, v_pack, v_params, group_size=128, num_bits=4,
+                           seqlen_k=None, num_splits=0) -> int:
+    """Bytes of workspace a decode call with these tensors needs."""
+    out = q
+    a = _decode_args(q, k_pack, k_params, v_pack, v_params, 1.0, group_size, num_bits,
+                     None, None, None, None, seqlen_k, out, None, num_splits)
+    with torch.cuda.device(q.device):
+        return int(_lib.load().bd_decode_workspace_bytes(C.byref(a)))
+
+
+def plan_splits(batch: int, nheads_k: int, max_seqlen: int, num_bits: int = 4, sm_count: int = 148,
+                ctas_per_sm: int = 0) -> int:
+    """Sequence splits the decode call picks on a device with ``sm_count`` SMs (pure host logic)."""
+    return int(_lib.load().bd_plan_splits(batch, nheads_k, max_seqlen, num_bits, sm_count, ctas_per_sm))
+
+
+def combine_partials(part_outs, part_lses, out_dtype: torch.dtype = torch.float16, return_lse: bool = False):
+    """Merge partial attention results with their log-sum-exp.
+
+    ``part_outs``: list of (b, 1, h, d) or (rows, d) fp32 tensors, each normalised
+    within its part (e.g. one per sequence shard, from ``fwd_kvcache_int(...,
+    out_dtype=torch.float32, return_lse=True)``); ``part_lses``: matching fp32 LSEs.
+    The tensors may live on peer GPUs as long as peer access is enabled; the
+    result is written on the first tensor's device.
+    """
+    n = len(part_outs)
+    _require(1 <= n <= _lib.BD_MAX_PARTS and len(part_lses) == n, f"need 1..{_lib.BD_MAX_PARTS} parts")
+    shape = part_outs[0].shape
+    d = shape[-1]
+    rows = part_outs[0].numel() // d
+    for o, l in zip(part_outs, part_lses):
+        _require(o.is_cuda and l.is_cuda and o.dtype == torch.float32 and l.dtype == torch.float32,
+                 "partials must be fp32 CUDA tensors")
+        _require(o.is_contiguous() and l.is_contiguous() and o.shape == shape and l.numel() == rows,
+                 "partials must be contiguous and of equal shape")
+    dev = part_outs[0].device
+    out = torch.empty(shape, dtype=out_dtype, device=dev)
+    lse = torch.empty(part_lses[0].shape, dtype=torch.float32, device=dev) if return_lse else None
+    po = (C.c_void_p * n)(*[o.data_ptr() for o in part_outs])
+    pl = (C.c_void_p * n)(*[l.data_ptr() for l in part_lses])
+    a = _lib.CombineArgs(n_parts=n, part_out=C.cast(po, C.POINTER(C.c_void_p)),
+                         part_lse=C.cast(pl, C.POINTER(C.c_void_p)), rows=rows, d=d,
+                         out=out.data_ptr(), lse=(lse.data_ptr() if lse is not None else None),
+                         out_dtype=_dtype_code(out_dtype))
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().bd_combine(C.byref(a), _stream(dev)), "bd_combine")
+    return (out, lse) if return_lse else out

@@ -1,0 +1,382 @@
+// C-ABI layer: argument checks, split planning, tensor-map construction and
+// kernel dispatch.  Takes the place of the reference's host API (reference:
+// csrc/bit_decode/decode_api.cpp:22-180 parameter marshalling, :234-299 split
+// heuristic and workspace, :301-441 decode entry, :517-603 pack entry), minus
+// everything that needs ATen: no tensors, no allocation, no device sync.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/bitdecode.h"
+#include "bd_kernels.h"
+
+namespace {
+
+using bd::DecodeParams;
+using bd::PackParams;
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+struct DeviceInfo {
+    bool ok = false;
+    int sm_count = 0;
+    int cc_major = 0;
+};
+
+int current_device_info(DeviceInfo &info) {
+    static DeviceInfo cache[64];
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return BD_ERR_CUDA;
+    if (dev < 0 || dev >= 64) return BD_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cache[dev].ok) {
+        int sm = 0, major = 0;
+        if (cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return BD_ERR_CUDA;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return BD_ERR_CUDA;
+        cache[dev].sm_count = sm;
+        cache[dev].cc_major = major;
+        cache[dev].ok = true;
+    }
+    info = cache[dev];
+    return BD_OK;
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time
+// dependency on libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+// 2-D map over 16-bit words: dim0 = contiguous words of one row (all heads),
+// dim1 = rows.  Box = (box_w words, box_rows rows).
+int make_map_2d(CUtensorMap *map, const void *base, uint64_t row_words, uint64_t rows, uint32_t box_w,
+                uint32_t box_rows, CUtensorMapSwizzle swz) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return BD_ERR_CUDA;
+    cuuint64_t dims[2] = {row_words, rows};
+    cuuint64_t strides[1] = {row_words * 2};
+    cuuint32_t box[2] = {box_w, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? BD_OK : BD_ERR_CUDA;
+}
+
+int pack_block_tokens(int bits) { return 32 * (16 / bits); }
+
+bool config_supported(int bits, int group, int d) {
+    return (bits == 2 || bits == 4) && (group == 64 || group == 128) && d == 128;
+}
+
+struct DecodePlan {
+    int num_splits;
+    int chunk_blocks;
+    size_t part_out_bytes, part_lse_bytes, total_bytes;
+};
+
+// Every CTA of the decode grid should be resident at once (one wave) and carry
+// the same number of pack blocks: then all of them stream at the same rate and
+// finish together.  Pick the largest split count whose grid still fits.
+int plan_splits(int b, int h_k, int64_t max_s, int bits, int sm_count, int ctas_per_sm) {
+    if (b <= 0 || h_k <= 0 || max_s <= 0) return 1;
+    const int nb = pack_block_tokens(bits);
+    const int64_t nblk = (max_s + nb - 1) / nb;
+    if (ctas_per_sm <= 0) ctas_per_sm = bd::decode_ctas_per_sm_default();
+    const int64_t slots = int64_t(sm_count) * ctas_per_sm;
+    const int64_t pairs = int64_t(b) * h_k;
+    int64_t splits = std::max<int64_t>(1, slots / pairs);
+    // at least 4 blocks per split (one per consumer warp), at most 128 splits
+    splits = std::min<int64_t>(splits, std::max<int64_t>(1, nblk / 4));
+    splits = std::min<int64_t>(splits, 128);
+    const int64_t chunk = (nblk + splits - 1) / splits;
+    return int((nblk + chunk - 1) / chunk);
+}
+
+int make_plan(const bd_decode_args *a, int sm_count, DecodePlan &plan) {
+    const int nb = pack_block_tokens(a->bits);
+    const int64_t nblk = std::max<int64_t>(1, (int64_t(a->s) + nb - 1) / nb);
+    int splits = a->num_splits > 0 ? a->num_splits : plan_splits(a->b, a->h_k, a->s, a->bits, sm_count, 0);
+    splits = int(std::min<int64_t>(splits, nblk));
+    splits = std::max(1, std::min(splits, 1024));
+    const int64_t chunk = (nblk + splits - 1) / splits;
+    plan.chunk_blocks = int(chunk);
+    plan.num_splits = int((nblk + chunk - 1) / chunk);
+    const size_t rows = size_t(a->b) * a->h;
+    plan.part_out_bytes = plan.num_splits > 1 ? rows * plan.num_splits * 128 * sizeof(float) : 0;
+    plan.part_lse_bytes = plan.num_splits > 1 ? ((rows * plan.num_splits * sizeof(float) + 15) / 16) * 16 : 0;
+    plan.total_bytes = plan.part_out_bytes + plan.part_lse_bytes + 16;
+    return BD_OK;
+}
+
+int check_decode_args(const bd_decode_args *a) {
+    if (!a || !a->q || !a->out || !a->k_pack || !a->k_params || !a->v_pack || !a->v_params) return BD_ERR_INVALID;
+    if (a->b <= 0 || a->h <= 0 || a->h_k <= 0 || a->s < 0 || a->s_cap <= 0) return BD_ERR_INVALID;
+    if (!config_supported(a->bits, a->group, a->d)) return BD_ERR_UNSUPPORTED;
+    if (a->dtype != BD_FP16 && a->dtype != BD_BF16) return BD_ERR_UNSUPPORTED;
+    if (a->out_dtype != BD_FP16 && a->out_dtype != BD_BF16 && a->out_dtype != BD_FP32) return BD_ERR_UNSUPPORTED;
+    if (a->h % a->h_k) return BD_ERR_INVALID;
+    if (a->h / a->h_k > 16) return BD_ERR_UNSUPPORTED;
+    const int nb = pack_block_tokens(a->bits);
+    if (a->s_cap % nb || a->s > a->s_cap) return BD_ERR_INVALID;
+    if ((a->k_res == nullptr) != (a->v_res == nullptr)) return BD_ERR_INVALID;
+    if (a->k_res && (a->res_len < 0 || a->res_len > 256)) return BD_ERR_UNSUPPORTED;
+    if (!aligned16(a->q) || !aligned16(a->out) || !aligned16(a->k_pack) || !aligned16(a->k_params) ||
+        !aligned16(a->v_pack) || !aligned16(a->v_params))
+        return BD_ERR_ALIGNMENT;
+    if (a->k_res && (!aligned16(a->k_res) || !aligned16(a->v_res))) return BD_ERR_ALIGNMENT;
+    if (a->q_stride_b % 8 || a->q_stride_h % 8 || a->out_stride_b % 4 || a->out_stride_h % 4) return BD_ERR_ALIGNMENT;
+    if (a->k_res && (a->res_stride_b % 8 || a->res_stride_s % 8 || a->res_stride_h % 8)) return BD_ERR_ALIGNMENT;
+    // pack buffers: whole rows per batch step so that TMA coordinates stay integral
+    const int64_t k_row = int64_t(a->h_k) * 128, v_row = int64_t(a->h_k) * (128 / (16 / a->bits));
+    if (a->k_pack_stride_b % k_row || a->v_pack_stride_b % v_row) return BD_ERR_ALIGNMENT;
+    if (a->k_params_stride_b % 4 || a->v_params_stride_b % 4 || a->v_params_stride_g % 4 || a->v_params_stride_h % 4)
+        return BD_ERR_ALIGNMENT;
+    return BD_OK;
+}
+
+// Small cache of encoded tensor maps: a decode loop calls with the same buffers
+// every step, and encoding costs a few microseconds of host time per map.
+struct MapKey {
+    const void *base;
+    uint64_t row_words, rows;
+    uint32_t box_w, box_rows;
+    int swz;
+    int dev;
+    bool operator==(const MapKey &o) const {
+        return base == o.base && row_words == o.row_words && rows == o.rows && box_w == o.box_w &&
+               box_rows == o.box_rows && swz == o.swz && dev == o.dev;
+    }
+};
+struct MapCache {
+    static constexpr int N = 32;
+    MapKey keys[N];
+    CUtensorMap maps[N];
+    bool used[N] = {};
+    int next = 0;
+    std::mutex mu;
+};
+
+int get_map(CUtensorMap *out, const void *base, uint64_t row_words, uint64_t rows, uint32_t box_w,
+            uint32_t box_rows, CUtensorMapSwizzle swz) {
+    static MapCache cache;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    MapKey key{base, row_words, rows, box_w, box_rows, int(swz), dev};
+    std::lock_guard<std::mutex> lock(cache.mu);
+    for (int i = 0; i < MapCache::N; ++i)
+        if (cache.used[i] && cache.keys[i] == key) {
+            *out = cache.maps[i];
+            return BD_OK;
+        }
+    CUtensorMap m;
+    int rc = make_map_2d(&m, base, row_words, rows, box_w, box_rows, swz);
+    if (rc != BD_OK) return rc;
+    const int slot = cache.next;
+    cache.next = (cache.next + 1) % MapCache::N;
+    cache.keys[slot] = key;
+    cache.maps[slot] = m;
+    cache.used[slot] = true;
+    *out = m;
+    return BD_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int bd_version(void) { return BD_VERSION; }
+
+const char *bd_strerror(int code) {
+    switch (code) {
+        case BD_OK: return "ok";
+        case BD_ERR_INVALID: return "invalid argument (null pointer, bad size or stride)";
+        case BD_ERR_UNSUPPORTED: return "unsupported configuration (bits must be 2 or 4, group 64 or 128, head_dim 128, "
+                                        "fp16/bf16, at most 16 query heads per KV head, tail of at most 256 tokens)";
+        case BD_ERR_ALIGNMENT: return "pointer or stride not aligned (16-byte pointers, strides in whole rows / multiples of 8)";
+        case BD_ERR_WORKSPACE: return "workspace missing or too small (see bd_decode_workspace_bytes)";
+        case BD_ERR_CUDA: return "a CUDA runtime or driver call failed";
+        case BD_ERR_DEVICE: return "device is not compute capability 10.x";
+        case BD_ERR_TIMEOUT: return "a bounded wait inside a kernel ran out";
+        default: return "unknown error";
+    }
+}
+
+int bd_plan_splits(int b, int h_k, int64_t max_s, int bits, int sm_count, int ctas_per_sm) {
+    if (bits != 2 && bits != 4) return 1;
+    return plan_splits(b, h_k, max_s, bits, sm_count, ctas_per_sm);
+}
+
+int bd_pack(const bd_pack_args *a, bd_stream_t stream) {
+    if (!a || !a->k || !a->v || !a->k_pack || !a->k_params || !a->v_pack || !a->v_params) return BD_ERR_INVALID;
+    if (a->b <= 0 || a->h_k <= 0 || a->s < 0 || a->dst_token_offset < 0) return BD_ERR_INVALID;
+    if (!config_supported(a->bits, a->group, a->d)) return BD_ERR_UNSUPPORTED;
+    if (a->dtype != BD_FP16 && a->dtype != BD_BF16) return BD_ERR_UNSUPPORTED;
+    const int nb = pack_block_tokens(a->bits);
+    if (a->s % nb || a->dst_token_offset % nb) return BD_ERR_INVALID;
+    if (a->h_k > 65535 || a->b > 65535) return BD_ERR_INVALID;
+    if ((reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v) |
+         reinterpret_cast<uintptr_t>(a->k_pack) | reinterpret_cast<uintptr_t>(a->v_pack) |
+         reinterpret_cast<uintptr_t>(a->k_params) | reinterpret_cast<uintptr_t>(a->v_params)) & 3u)
+        return BD_ERR_ALIGNMENT;
+    if ((a->k_stride_b | a->k_stride_s | a->k_stride_h | a->v_stride_b | a->v_stride_s | a->v_stride_h |
+         a->k_pack_stride_b | a->v_pack_stride_b) & 1)
+        return BD_ERR_ALIGNMENT;
+    if (a->s == 0) return BD_OK;
+    DeviceInfo info;
+    int rc = current_device_info(info);
+    if (rc != BD_OK) return rc;
+    if (info.cc_major != 10) return BD_ERR_DEVICE;
+    PackParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.k = a->k; p.v = a->v;
+    p.k_stride_b = a->k_stride_b; p.k_stride_s = a->k_stride_s; p.k_stride_h = a->k_stride_h;
+    p.v_stride_b = a->v_stride_b; p.v_stride_s = a->v_stride_s; p.v_stride_h = a->v_stride_h;
+    p.k_pack = a->k_pack; p.k_params = a->k_params; p.v_pack = a->v_pack; p.v_params = a->v_params;
+    p.k_pack_stride_b = a->k_pack_stride_b; p.k_params_stride_b = a->k_params_stride_b;
+    p.v_pack_stride_b = a->v_pack_stride_b;
+    p.v_params_stride_b = a->v_params_stride_b; p.v_params_stride_g = a->v_params_stride_g;
+    p.v_params_stride_h = a->v_params_stride_h;
+    p.b = a->b; p.s = a->s; p.h_k = a->h_k; p.dst_token_offset = a->dst_token_offset;
+    cudaError_t err = bd::launch_pack(p, a->bits, a->group, a->dtype, static_cast<cudaStream_t>(stream));
+    return err == cudaSuccess ? BD_OK : BD_ERR_CUDA;
+}
+
+size_t bd_decode_workspace_bytes(const bd_decode_args *a) {
+    if (!a || a->b <= 0 || a->h <= 0 || a->h_k <= 0 || (a->bits != 2 && a->bits != 4)) return 0;
+    DeviceInfo info;
+    int sm = 148;
+    if (a->num_splits <= 0) {
+        if (current_device_info(info) != BD_OK) return 0;
+        sm = info.sm_count;
+    }
+    DecodePlan plan;
+    make_plan(a, sm, plan);
+    return plan.total_bytes;
+}
+
+int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
+    int rc = check_decode_args(a);
+    if (rc != BD_OK) return rc;
+    DeviceInfo info;
+    rc = current_device_info(info);
+    if (rc != BD_OK) return rc;
+    if (info.cc_major != 10) return BD_ERR_DEVICE;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+    DecodePlan plan;
+    make_plan(a, info.sm_count, plan);
+    if (!a->workspace || a->workspace_bytes < plan.total_bytes) return BD_ERR_WORKSPACE;
+    if (!aligned16(a->workspace)) return BD_ERR_ALIGNMENT;
+    if (a->b > 65535 || plan.num_splits > 65535) return BD_ERR_INVALID;
+
+    const int P = 16 / a->bits, nb = 32 * P, dp = 128 / P;
+    const int64_t k_row = int64_t(a->h_k) * 128, v_row = int64_t(a->h_k) * dp;
+    const int64_t k_batch_rows = a->k_pack_stride_b / k_row, v_batch_rows = a->v_pack_stride_b / v_row;
+    const uint64_t k_rows_total = uint64_t(a->b - 1) * k_batch_rows + uint64_t(a->s_cap / P);
+    const uint64_t v_rows_total = uint64_t(a->b - 1) * v_batch_rows + uint64_t(a->s_cap);
+    if (k_rows_total > 0x7fffffffull || v_rows_total > 0x7fffffffull) return BD_ERR_INVALID;
+
+    CUtensorMap kmap, vmap;
+    rc = get_map(&kmap, a->k_pack, uint64_t(k_row), k_rows_total, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != BD_OK) return rc;
+    rc = get_map(&vmap, a->v_pack, uint64_t(v_row), v_rows_total, uint32_t(dp), uint32_t(nb),
+                 a->bits == 4 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    if (rc != BD_OK) return rc;
+
+    uint8_t *ws = static_cast<uint8_t *>(a->workspace);
+    DecodeParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.q = a->q; p.out = a->out; p.lse = a->lse;
+    p.q_stride_b = a->q_stride_b; p.q_stride_h = a->q_stride_h;
+    p.out_stride_b = a->out_stride_b; p.out_stride_h = a->out_stride_h;
+    p.k_params = static_cast<const uint16_t *>(a->k_params);
+    p.v_params = static_cast<const uint16_t *>(a->v_params);
+    p.k_params_stride_b = 2 * a->k_params_stride_b;
+    p.v_params_stride_b = 2 * a->v_params_stride_b;
+    p.v_params_stride_g = 2 * a->v_params_stride_g;
+    p.v_params_stride_h = 2 * a->v_params_stride_h;
+    p.cache_seqlens = a->cache_seqlens;
+    p.k_res = a->k_res; p.v_res = a->v_res;
+    p.res_stride_b = a->res_stride_b; p.res_stride_s = a->res_stride_s; p.res_stride_h = a->res_stride_h;
+    p.res_lens = a->res_lens; p.res_len = a->k_res ? a->res_len : 0;
+    p.b = a->b; p.h = a->h; p.h_k = a->h_k; p.gq = a->h / a->h_k;
+    p.s = a->s;
+    p.chunk_blocks = plan.chunk_blocks;
+    p.num_splits = plan.num_splits;
+    p.k_batch_rows = int32_t(k_batch_rows);
+    p.v_batch_rows = int32_t(v_batch_rows);
+    p.dtype = a->dtype; p.out_dtype = a->out_dtype;
+    p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+    // workspace: [status word, 16 B][partial outputs][partial LSEs]
+    p.status = reinterpret_cast<int32_t *>(ws);
+    p.part_out = reinterpret_cast<float *>(ws + 16);
+    p.part_lse = reinterpret_cast<float *>(ws + 16 + plan.part_out_bytes);
+
+    cudaError_t err = cudaMemsetAsync(p.status, 0, sizeof(int32_t), stream);
+    if (err != cudaSuccess) return BD_ERR_CUDA;
+    err = bd::launch_decode(p, kmap, vmap, a->bits, a->group, stream);
+    if (err != cudaSuccess) return BD_ERR_CUDA;
+    if (plan.num_splits > 1) {
+        bd::CombineSplitParams c;
+        std::memset(&c, 0, sizeof(c));
+        c.part_out = p.part_out; c.part_lse = p.part_lse;
+        c.out = a->out; c.lse = a->lse;
+        c.out_stride_b = a->out_stride_b; c.out_stride_h = a->out_stride_h;
+        c.cache_seqlens = a->cache_seqlens;
+        c.b = a->b; c.h = a->h; c.s = a->s;
+        c.num_splits = plan.num_splits;
+        c.chunk_tokens = plan.chunk_blocks * nb;
+        c.out_dtype = a->out_dtype;
+        err = bd::launch_combine_splits(c, stream);
+        if (err != cudaSuccess) return BD_ERR_CUDA;
+    }
+    return BD_OK;
+}
+
+int bd_combine(const bd_combine_args *a, bd_stream_t stream) {
+    if (!a || !a->part_out || !a->part_lse || !a->out) return BD_ERR_INVALID;
+    if (a->n_parts < 1 || a->n_parts > BD_MAX_PARTS || a->rows <= 0) return BD_ERR_INVALID;
+    if (a->d != 128) return BD_ERR_UNSUPPORTED;
+    if (a->out_dtype != BD_FP16 && a->out_dtype != BD_BF16 && a->out_dtype != BD_FP32) return BD_ERR_UNSUPPORTED;
+    if (!aligned16(a->out)) return BD_ERR_ALIGNMENT;
+    bd::CombinePartsParams p;
+    std::memset(&p, 0, sizeof(p));
+    for (int i = 0; i < a->n_parts; ++i) {
+        if (!a->part_out[i] || !a->part_lse[i]) return BD_ERR_INVALID;
+        if (!aligned16(a->part_out[i])) return BD_ERR_ALIGNMENT;
+        p.part_out[i] = a->part_out[i];
+        p.part_lse[i] = a->part_lse[i];
+    }
+    p.out = a->out; p.lse = a->lse; p.rows = a->rows; p.n_parts = a->n_parts; p.out_dtype = a->out_dtype;
+    cudaError_t err = bd::launch_combine_parts(p, static_cast<cudaStream_t>(stream));
+    return err == cudaSuccess ? BD_OK : BD_ERR_CUDA;
+}
+
+int bd_read_status(const void *workspace, bd_stream_t stream) {
+    if (!workspace) return BD_ERR_INVALID;
+    if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) return BD_ERR_CUDA;
+    int32_t v = 0;   // the status word is the first word of the workspace
+    if (cudaMemcpy(&v, workspace, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return BD_ERR_CUDA;
+    return v;
+}
+
+}  // extern "C"

@@ -1,0 +1,119 @@
+// Log-sum-exp merge of partial attention results.
+//
+//   LSE = log sum_i exp(lse_i),   out = sum_i exp(lse_i - LSE) * out_i
+//
+// Same arithmetic as the reference's split combine (reference:
+// csrc/bit_decode/src/flash_fwd_kernel.h:1217-1231 for the LSE, :1280-1298 for
+// the weighted sum).  One warp per (batch, query head) row, each lane owns four
+// consecutive head dims (one 16-byte load per partial).
+//
+// Two variants: the split combine reads the partials bd_decode left in its
+// workspace (and knows how many splits each sequence really has); the parts
+// combine takes one pointer per part, which may point into another GPU's memory
+// (plain loads over NVLink, no multicast, no TMA).
+#include "bd_common.cuh"
+#include "bd_kernels.h"
+
+namespace bd {
+
+constexpr int kCombineWarps = 4;
+
+__device__ __forceinline__ void store_out4(void *out, int64_t idx, const float (&o)[4], int out_dtype) {
+    if (out_dtype == BD_FP16) {
+        __half2 a = __floats2half2_rn(o[0], o[1]), b = __floats2half2_rn(o[2], o[3]);
+        uint2 w = make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b));
+        *reinterpret_cast<uint2 *>(static_cast<__half *>(out) + idx) = w;
+    } else if (out_dtype == BD_BF16) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(o[0], o[1]), b = __floats2bfloat162_rn(o[2], o[3]);
+        uint2 w = make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b));
+        *reinterpret_cast<uint2 *>(static_cast<__nv_bfloat16 *>(out) + idx) = w;
+    } else {
+        *reinterpret_cast<float4 *>(static_cast<float *>(out) + idx) = make_float4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+__global__ void __launch_bounds__(kCombineWarps * 32)
+bd_combine_splits_kernel(const CombineSplitParams p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row = int64_t(blockIdx.x) * kCombineWarps + warp;
+    if (row >= int64_t(p.b) * p.h) return;
+    const int ib = int(row / p.h), hq = int(row % p.h);
+    int seqlen = p.s;
+    if (p.cache_seqlens) seqlen = min(max(p.cache_seqlens[ib], 0), p.s);
+    int n = max(1, (seqlen + p.chunk_tokens - 1) / p.chunk_tokens);
+    n = min(n, p.num_splits);
+    const float *lse_in = p.part_lse + row * p.num_splits;
+    const float *out_in = p.part_out + row * p.num_splits * kHeadDim;
+
+    float mx = -INFINITY;
+    for (int s = lane; s < n; s += 32) mx = fmaxf(mx, lse_in[s]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    float sum = 0.f;
+    if (mx != -INFINITY)
+        for (int s = lane; s < n; s += 32) sum += __expf(lse_in[s] - mx);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    const float lse = (sum > 0.f) ? mx + logf(sum) : -INFINITY;
+
+    float o[4] = {0.f, 0.f, 0.f, 0.f};
+    if (sum > 0.f) {
+        for (int s = 0; s < n; ++s) {
+            const float w = __expf(lse_in[s] - lse);
+            const float4 v = *reinterpret_cast<const float4 *>(out_in + int64_t(s) * kHeadDim + 4 * lane);
+            o[0] = fmaf(w, v.x, o[0]); o[1] = fmaf(w, v.y, o[1]);
+            o[2] = fmaf(w, v.z, o[2]); o[3] = fmaf(w, v.w, o[3]);
+        }
+    }
+    store_out4(p.out, ib * p.out_stride_b + int64_t(hq) * p.out_stride_h + 4 * lane, o, p.out_dtype);
+    if (lane == 0 && p.lse) p.lse[row] = lse;
+}
+
+__global__ void __launch_bounds__(kCombineWarps * 32)
+bd_combine_parts_kernel(const CombinePartsParams p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row = int64_t(blockIdx.x) * kCombineWarps + warp;
+    if (row >= p.rows) return;
+    float l[16];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        l[i] = (i < p.n_parts) ? p.part_lse[i][row] : -INFINITY;
+        mx = fmaxf(mx, l[i]);
+    }
+    float sum = 0.f;
+    if (mx != -INFINITY) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) sum += (i < p.n_parts) ? __expf(l[i] - mx) : 0.f;
+    }
+    const float lse = (sum > 0.f) ? mx + logf(sum) : -INFINITY;
+    float o[4] = {0.f, 0.f, 0.f, 0.f};
+    if (sum > 0.f) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if (i < p.n_parts) {
+                const float w = __expf(l[i] - lse);
+                const float4 v = *reinterpret_cast<const float4 *>(p.part_out[i] + row * kHeadDim + 4 * lane);
+                o[0] = fmaf(w, v.x, o[0]); o[1] = fmaf(w, v.y, o[1]);
+                o[2] = fmaf(w, v.z, o[2]); o[3] = fmaf(w, v.w, o[3]);
+            }
+        }
+    }
+    store_out4(p.out, row * kHeadDim + 4 * lane, o, p.out_dtype);
+    if (lane == 0 && p.lse) p.lse[row] = lse;
+}
+
+cudaError_t launch_combine_splits(const CombineSplitParams &p, cudaStream_t stream) {
+    const int64_t rows = int64_t(p.b) * p.h;
+    const unsigned grid = unsigned((rows + kCombineWarps - 1) / kCombineWarps);
+    bd_combine_splits_kernel<<<grid, kCombineWarps * 32, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_combine_parts(const CombinePartsParams &p, cudaStream_t stream) {
+    const unsigned grid = unsigned((p.rows + kCombineWarps - 1) / kCombineWarps);
+    bd_combine_parts_kernel<<<grid, kCombineWarps * 32, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace bd

@@ -1,0 +1,243 @@
+// Quantize-pack kernel: K per channel (groups of G consecutive tokens), V per
+// token (groups of G consecutive dims), asymmetric min-max to 4 or 2 bits.
+//
+// Arithmetic follows the reference quantizer step by step in IEEE fp32
+// (reference: csrc/bit_decode/src/include/qpack.h:241-252 for range, scale_inv,
+// stored scale and zero; :266-281 for subtract, multiply, roundf, clamp; :283-294
+// for the field order inside a word).  Explicit round-to-nearest intrinsics keep
+// the result independent of compiler flags, so codes, scales and zeros are
+// bit-identical to a CPU evaluation of the same formulas.
+//
+// One CTA handles one pack block (NB = 32 * 16/bits tokens) of one KV head.
+// The work is pure streaming (read 2*NB*d*2 bytes, write a quarter or an eighth
+// of that): every thread keeps 64 packed pairs in flight for K, rows are read
+// and written in 128-byte warp segments, and nothing is re-read.
+#include "bd_common.cuh"
+#include "bd_kernels.h"
+
+namespace bd {
+
+template <bool BF16>
+__device__ __forceinline__ float2 pair_to_float2(uint32_t w) {
+    if constexpr (BF16) {
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    } else {
+        return __half22float2(*reinterpret_cast<__half2 *>(&w));
+    }
+}
+
+// roundf() for v >= 0 (ties away from zero).  v - trunc(v) is exact, so the
+// comparison sees the true fraction; NaN falls through to the clamp like the
+// reference's fmaxf(roundf(NaN), 0) = 0.
+__device__ __forceinline__ uint32_t quant_code(float x, float mn, float scale_inv, float maxv) {
+    float v = __fmul_rn(__fsub_rn(x, mn), scale_inv);
+    float r = truncf(v);
+    r = __fadd_rn(r, (__fsub_rn(v, r) >= 0.5f) ? 1.0f : 0.0f);
+    r = fminf(fmaxf(r, 0.0f), maxv);
+    return static_cast<uint32_t>(r);
+}
+
+__device__ __forceinline__ void scale_from_minmax(float mn, float mx, float maxv, float &scale_inv, float &scale) {
+    const float range = __fsub_rn(mx, mn);
+    scale_inv = (range > 0.0f) ? __fdiv_rn(maxv, range) : 0.0f;
+    scale = (scale_inv == 0.0f) ? 0.0f : __fdiv_rn(1.0f, scale_inv);
+}
+
+template <int BITS, int GROUP, bool BF16>
+__global__ void __launch_bounds__(64 * (32 * (16 / BITS) / 64))
+bd_pack_kernel(const PackParams p) {
+    constexpr int P = 16 / BITS;            // codes per 16-bit word
+    constexpr int NB = 32 * P;              // tokens per pack block
+    constexpr int NT = NB / 64;             // token subsets (threads = 64 * NT)
+    constexpr int NTHREADS = 64 * NT;
+    constexpr int PPT = 32 / NT;            // pack rows per thread (K)
+    constexpr int NGK = NB / GROUP;         // K token groups per block
+    constexpr int FPG = GROUP / 32;         // K fields per group
+    constexpr int D = kHeadDim;
+    constexpr int DP = D / P;               // words per V row
+    constexpr int NGD = D / GROUP;          // V dim groups
+    constexpr int FPGV = P / NGD;           // V fields per dim group
+    constexpr int LPT = DP / 2;             // lanes per token (V)
+    constexpr int TPI = NTHREADS / LPT;     // tokens per iteration (V)
+    constexpr int VITER = NB / TPI;
+    constexpr int VU = (VITER >= 4) ? 4 : VITER;   // V iterations loaded together
+    const float maxv = static_cast<float>((1 << BITS) - 1);
+
+    __shared__ float red[NT][NGK][2][D];
+    __shared__ __half vprm[NGD][2][NB];
+
+    const int tid = threadIdx.x;
+    const int blk = blockIdx.x, ih = blockIdx.y, ib = blockIdx.z;
+    const int dst_blk = blk + p.dst_token_offset / NB;
+    const uint16_t *kin = static_cast<const uint16_t *>(p.k);
+    const uint16_t *vin = static_cast<const uint16_t *>(p.v);
+
+    // ------------------------------------------------------------------ K
+    {
+        const int cp = tid & 63, T = tid >> 6;
+        const uint16_t *kbase = kin + ib * p.k_stride_b + static_cast<int64_t>(blk) * NB * p.k_stride_s +
+                                ih * p.k_stride_h + 2 * cp;
+        uint32_t raw[PPT][P];
+#pragma unroll
+        for (int pi = 0; pi < PPT; ++pi)
+#pragma unroll
+            for (int j = 0; j < P; ++j) {
+                const int t = T * PPT + pi + 32 * j;
+                raw[pi][j] = __ldg(reinterpret_cast<const unsigned int *>(kbase + t * p.k_stride_s));
+            }
+        float mn[NGK][2], mx[NGK][2];
+#pragma unroll
+        for (int gk = 0; gk < NGK; ++gk) {
+            mn[gk][0] = mn[gk][1] = INFINITY;
+            mx[gk][0] = mx[gk][1] = -INFINITY;
+        }
+#pragma unroll
+        for (int pi = 0; pi < PPT; ++pi)
+#pragma unroll
+            for (int j = 0; j < P; ++j) {
+                const float2 x = pair_to_float2<BF16>(raw[pi][j]);
+                const int gk = j / FPG;
+                mn[gk][0] = fminf(mn[gk][0], x.x); mx[gk][0] = fmaxf(mx[gk][0], x.x);
+                mn[gk][1] = fminf(mn[gk][1], x.y); mx[gk][1] = fmaxf(mx[gk][1], x.y);
+            }
+#pragma unroll
+        for (int gk = 0; gk < NGK; ++gk) {
+            red[T][gk][0][2 * cp] = mn[gk][0]; red[T][gk][0][2 * cp + 1] = mn[gk][1];
+            red[T][gk][1][2 * cp] = mx[gk][0]; red[T][gk][1][2 * cp + 1] = mx[gk][1];
+        }
+        __syncthreads();
+        float sinv[NGK][2];
+#pragma unroll
+        for (int gk = 0; gk < NGK; ++gk)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float a = red[0][gk][0][2 * cp + e], b = red[0][gk][1][2 * cp + e];
+#pragma unroll
+                for (int t2 = 1; t2 < NT; ++t2) {
+                    a = fminf(a, red[t2][gk][0][2 * cp + e]);
+                    b = fmaxf(b, red[t2][gk][1][2 * cp + e]);
+                }
+                mn[gk][e] = a;
+                float sc;
+                scale_from_minmax(a, b, maxv, sinv[gk][e], sc);
+                mx[gk][e] = sc;   // reuse as the stored scale
+            }
+        if (T == 0) {
+#pragma unroll
+            for (int gk = 0; gk < NGK; ++gk) {
+                const int64_t grow = static_cast<int64_t>(dst_blk) * NGK + gk;
+                __half *prm = reinterpret_cast<__half *>(p.k_params) +
+                              2 * (ib * p.k_params_stride_b + (grow * p.h_k + ih) * D);
+                *reinterpret_cast<__half2 *>(prm + 2 * cp) = __floats2half2_rn(mx[gk][0], mx[gk][1]);
+                *reinterpret_cast<__half2 *>(prm + D + 2 * cp) = __floats2half2_rn(mn[gk][0], mn[gk][1]);
+            }
+        }
+        uint16_t *kp = static_cast<uint16_t *>(p.k_pack) + ib * p.k_pack_stride_b +
+                       ((static_cast<int64_t>(dst_blk) * 32 + T * PPT) * p.h_k + ih) * D + 2 * cp;
+#pragma unroll
+        for (int pi = 0; pi < PPT; ++pi) {
+            uint32_t lo = 0, hi = 0;
+#pragma unroll
+            for (int j = 0; j < P; ++j) {
+                const float2 x = pair_to_float2<BF16>(raw[pi][j]);
+                const int gk = j / FPG;
+                lo |= quant_code(x.x, mn[gk][0], sinv[gk][0], maxv) << (BITS * j);
+                hi |= quant_code(x.y, mn[gk][1], sinv[gk][1], maxv) << (BITS * j);
+            }
+            *reinterpret_cast<uint32_t *>(kp + static_cast<int64_t>(pi) * p.h_k * D) = lo | (hi << 16);
+        }
+    }
+
+    // ------------------------------------------------------------------ V
+    {
+        const int li = tid % LPT, tsub = tid / LPT;
+        const uint16_t *vbase = vin + ib * p.v_stride_b + static_cast<int64_t>(blk) * NB * p.v_stride_s +
+                                ih * p.v_stride_h + 2 * li;
+        uint16_t *vp = static_cast<uint16_t *>(p.v_pack) + ib * p.v_pack_stride_b +
+                       (static_cast<int64_t>(dst_blk) * NB * p.h_k + ih) * DP + 2 * li;
+#pragma unroll 1
+        for (int it0 = 0; it0 < VITER; it0 += VU) {
+            uint32_t raw[VU][P];
+#pragma unroll
+            for (int u = 0; u < VU; ++u) {
+                const int t = (it0 + u) * TPI + tsub;
+#pragma unroll
+                for (int j = 0; j < P; ++j)
+                    raw[u][j] = __ldg(reinterpret_cast<const unsigned int *>(vbase + t * p.v_stride_s + DP * j));
+            }
+#pragma unroll
+            for (int u = 0; u < VU; ++u) {
+                const int t = (it0 + u) * TPI + tsub;
+                float mn[NGD], mx[NGD];
+#pragma unroll
+                for (int gd = 0; gd < NGD; ++gd) { mn[gd] = INFINITY; mx[gd] = -INFINITY; }
+#pragma unroll
+                for (int j = 0; j < P; ++j) {
+                    const float2 x = pair_to_float2<BF16>(raw[u][j]);
+                    const int gd = j / FPGV;
+                    mn[gd] = fminf(mn[gd], fminf(x.x, x.y));
+                    mx[gd] = fmaxf(mx[gd], fmaxf(x.x, x.y));
+                }
+                float sinv[NGD];
+#pragma unroll
+                for (int gd = 0; gd < NGD; ++gd) {
+#pragma unroll
+                    for (int off = 1; off < LPT; off <<= 1) {
+                        mn[gd] = fminf(mn[gd], __shfl_xor_sync(0xffffffffu, mn[gd], off));
+                        mx[gd] = fmaxf(mx[gd], __shfl_xor_sync(0xffffffffu, mx[gd], off));
+                    }
+                    float sc;
+                    scale_from_minmax(mn[gd], mx[gd], maxv, sinv[gd], sc);
+                    if (li == 0) {
+                        vprm[gd][0][t] = __float2half_rn(sc);
+                        vprm[gd][1][t] = __float2half_rn(mn[gd]);
+                    }
+                }
+                uint32_t lo = 0, hi = 0;
+#pragma unroll
+                for (int j = 0; j < P; ++j) {
+                    const float2 x = pair_to_float2<BF16>(raw[u][j]);
+                    const int gd = j / FPGV;
+                    lo |= quant_code(x.x, mn[gd], sinv[gd], maxv) << (BITS * j);
+                    hi |= quant_code(x.y, mn[gd], sinv[gd], maxv) << (BITS * j);
+                }
+                *reinterpret_cast<uint32_t *>(vp + static_cast<int64_t>(t) * p.h_k * DP) = lo | (hi << 16);
+            }
+        }
+        __syncthreads();
+        // scales / zeros of this block's tokens: per dim group, per run of 128 tokens,
+        // 128 scales then 128 zeros.
+        constexpr int RUNS = NB / 128;
+        const int64_t run0 = static_cast<int64_t>(dst_blk) * RUNS;
+        for (int i = tid; i < NGD * RUNS * 2 * 64; i += NTHREADS) {
+            const int w = i & 63;                  // pair index inside 128 values
+            const int z = (i >> 6) & 1;            // 0 scales, 1 zeros
+            const int run = (i >> 7) % RUNS;
+            const int gd = (i >> 7) / RUNS;
+            __half *dst = reinterpret_cast<__half *>(p.v_params) +
+                          2 * (ib * p.v_params_stride_b + gd * p.v_params_stride_g + ih * p.v_params_stride_h) +
+                          256 * (run0 + run) + 128 * z + 2 * w;
+            *reinterpret_cast<__half2 *>(dst) = *reinterpret_cast<const __half2 *>(&vprm[gd][z][128 * run + 2 * w]);
+        }
+    }
+}
+
+template <int BITS, int GROUP, bool BF16>
+static cudaError_t launch_pack_t(const PackParams &p, cudaStream_t stream) {
+    constexpr int NB = 32 * (16 / BITS);
+    constexpr int NTHREADS = 64 * (NB / 64);
+    dim3 grid(p.s / NB, p.h_k, p.b);
+    bd_pack_kernel<BITS, GROUP, BF16><<<grid, NTHREADS, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_pack(const PackParams &p, int bits, int group, int dtype, cudaStream_t stream) {
+    const bool bf = dtype == BD_BF16;
+    if (bits == 4 && group == 128) return bf ? launch_pack_t<4, 128, true>(p, stream) : launch_pack_t<4, 128, false>(p, stream);
+    if (bits == 4 && group == 64)  return bf ? launch_pack_t<4, 64, true>(p, stream)  : launch_pack_t<4, 64, false>(p, stream);
+    if (bits == 2 && group == 128) return bf ? launch_pack_t<2, 128, true>(p, stream) : launch_pack_t<2, 128, false>(p, stream);
+    if (bits == 2 && group == 64)  return bf ? launch_pack_t<2, 64, true>(p, stream)  : launch_pack_t<2, 64, false>(p, stream);
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace bd

@@ -1,0 +1,182 @@
+/*
+ * bitdecode.h — C ABI of the B200-native low-bit KV-cache decode-attention library.
+ *
+ * One shared library (libbitdecode.so), plain pointers and sizes, no C++ or
+ * PyTorch types.  Every entry point returns 0 (BD_OK) or a negative BD_ERR_*
+ * code, never throws, never allocates device memory, never synchronises the
+ * device and launches its kernels on the stream it is given.  All pointers in
+ * the argument structs are device pointers unless stated otherwise.
+ *
+ * The entry points replace the four functions the reference exports from its
+ * pybind11 module `bit_decode_cuda` (reference: csrc/bit_decode/decode_api.cpp:605-611):
+ *
+ *   kvcache_pack_i2 / kvcache_pack_i4   ->  bd_pack    (bits = 2 / 4)
+ *   fwd_kvcache_i2  / fwd_kvcache_i4    ->  bd_decode  (bits = 2 / 4)
+ *
+ * Packed layouts (P = 16/bits codes per 16-bit word, NB = 32*P tokens per pack
+ * block, G = group size, d = head dim = 128):
+ *
+ *   k_pack   (b, s/P, h_k, d)   u16   word [32*blk + p][c], field j = token NB*blk + p + 32*j
+ *   k_params (b, s/G, h_k, d)   f32-sized slots holding 2*d fp16: [0:d] scale, [d:2d] zero
+ *   v_pack   (b, s, h_k, d/P)   u16   word [t][p], field j = dim p + (d/P)*j
+ *   v_params (b, d/G, h_k, s)   f32-sized slots holding 2*s fp16: per run of 128 tokens,
+ *                                     128 scales then 128 zeros
+ *
+ * For bits = 4, G = 128 these are byte-identical to what the reference's
+ * kernels write (reference: csrc/bit_decode/src/include/qpack.h:283-294 and
+ * csrc/bit_decode/src/flash_fwd_kernel.h:939-957).
+ */
+#ifndef BITDECODE_H_
+#define BITDECODE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BD_VERSION 100
+
+/* status codes */
+#define BD_OK                0
+#define BD_ERR_INVALID      -1   /* null pointer, non-positive size, bad stride */
+#define BD_ERR_UNSUPPORTED  -2   /* (bits, group, dtype, head_dim, GQA ratio) not built */
+#define BD_ERR_ALIGNMENT    -3   /* pointer or stride breaks a 16-byte / block rule */
+#define BD_ERR_WORKSPACE    -4   /* workspace missing or too small */
+#define BD_ERR_CUDA         -5   /* a CUDA runtime / driver call failed */
+#define BD_ERR_DEVICE       -6   /* not an sm_100 device */
+#define BD_ERR_TIMEOUT      -7   /* a bounded device-side wait ran out (see bd_read_status) */
+
+/* element types */
+#define BD_FP16 0
+#define BD_BF16 1
+#define BD_FP32 2   /* output only */
+
+typedef void *bd_stream_t;   /* a cudaStream_t */
+
+/*
+ * Quantize-pack.  Replaces kvcache_pack_i2 / kvcache_pack_i4
+ * (reference: csrc/bit_decode/decode_api.cpp:517-603, launch at
+ * csrc/bit_decode/src/flash_fwd_launch_template.h:224-250, kernel body
+ * csrc/bit_decode/src/flash_fwd_kernel.h:732-1091, quantizer
+ * csrc/bit_decode/src/include/qpack.h:110-300).
+ *
+ * Reads `s` tokens of K and V (s a multiple of NB) and writes their codes,
+ * scales and zeros into the pack buffers starting at token `dst_token_offset`
+ * (a multiple of NB).  Strides are in elements of the tensor they belong to;
+ * the innermost dimension of every tensor is contiguous.
+ */
+typedef struct bd_pack_args {
+    const void *k;            /* (b, s, h_k, d) fp16 or bf16 */
+    const void *v;
+    int64_t k_stride_b, k_stride_s, k_stride_h;
+    int64_t v_stride_b, v_stride_s, v_stride_h;
+    void *k_pack;             /* (b, s_cap/P, h_k, d) u16, rows contiguous */
+    void *k_params;           /* (b, s_cap/G, h_k, d) 4-byte slots */
+    void *v_pack;             /* (b, s_cap, h_k, d/P) u16 */
+    void *v_params;           /* (b, d/G, h_k, s_cap) 4-byte slots */
+    int64_t k_pack_stride_b, k_params_stride_b, v_pack_stride_b;
+    int64_t v_params_stride_b, v_params_stride_g, v_params_stride_h;
+    int32_t b, s, h_k, d;
+    int32_t dst_token_offset;
+    int32_t bits;             /* 2 or 4 */
+    int32_t group;            /* 64 or 128 */
+    int32_t dtype;            /* BD_FP16 or BD_BF16 */
+} bd_pack_args;
+
+int bd_pack(const bd_pack_args *args, bd_stream_t stream);
+
+/*
+ * One decode-attention step over the packed cache.  Replaces fwd_kvcache_i2 /
+ * fwd_kvcache_i4 (reference: csrc/bit_decode/decode_api.cpp:301-441; split-KV
+ * launch csrc/bit_decode/src/flash_fwd_launch_template.h:103-146, kernel body
+ * csrc/bit_decode/src/flash_fwd_kernel.h:66-728; combine kernel
+ * flash_fwd_launch_template.h:147-171, flash_fwd_kernel.h:1144-1327).
+ *
+ * out = softmax(scale * q K^T) V with one query token per sequence, over the
+ * first cache_seqlens[b] (or `s`) quantized tokens followed by the first
+ * res_lens[b] (or `res_len`) tokens of an unquantized tail, one joint softmax.
+ * Query head hq reads KV head hq / (h / h_k).  The reference has neither the
+ * tail, nor per-sequence lengths, nor a returned LSE; they are extensions.
+ *
+ * The workspace (bd_decode_workspace_bytes) holds the per-split partial
+ * results and one status word; the same workspace must not be used by two
+ * decode calls that can overlap on the device.
+ */
+typedef struct bd_decode_args {
+    const void *q;            /* (b, h, d) fp16 / bf16 */
+    void *out;                /* (b, h, d) in out_dtype */
+    float *lse;               /* optional (b, h): natural-log LSE of the scaled scores */
+    int64_t q_stride_b, q_stride_h;
+    int64_t out_stride_b, out_stride_h;
+    const void *k_pack, *k_params, *v_pack, *v_params;
+    int64_t k_pack_stride_b, k_params_stride_b, v_pack_stride_b;
+    int64_t v_params_stride_b, v_params_stride_g, v_params_stride_h;
+    const int32_t *cache_seqlens;   /* optional (b): quantized tokens valid per sequence */
+    const void *k_res;        /* optional (b, res_cap, h_k, d), same dtype as q */
+    const void *v_res;
+    int64_t res_stride_b, res_stride_s, res_stride_h;
+    const int32_t *res_lens;  /* optional (b): tail tokens valid per sequence */
+    int32_t res_len;          /* tail length when res_lens is null (0 = no tail) */
+    int32_t b, h, h_k, d;
+    int32_t s;                /* quantized tokens (upper bound when cache_seqlens is given) */
+    int32_t s_cap;            /* token capacity of the pack buffers, a multiple of NB */
+    int32_t bits, group;
+    int32_t dtype;            /* of q and the tail: BD_FP16 / BD_BF16 */
+    int32_t out_dtype;        /* BD_FP16 / BD_BF16 / BD_FP32 */
+    float softmax_scale;
+    int32_t num_splits;       /* 0 = choose (bd_plan_splits) */
+    void *workspace;
+    size_t workspace_bytes;
+} bd_decode_args;
+
+int bd_decode(const bd_decode_args *args, bd_stream_t stream);
+
+/* Bytes of workspace bd_decode needs for these arguments (0 on invalid input). */
+size_t bd_decode_workspace_bytes(const bd_decode_args *args);
+
+/*
+ * Number of sequence splits bd_decode uses when num_splits == 0; replaces
+ * num_splits_heuristic (reference: csrc/bit_decode/decode_api.cpp:234-268).
+ * `ctas_per_sm` <= 0 selects the library default.
+ */
+int bd_plan_splits(int b, int h_k, int64_t max_s, int bits, int sm_count, int ctas_per_sm);
+
+/*
+ * Merge n partial results (each normalised within its part) with their
+ * log-sum-exp: LSE = log sum_i exp(lse_i), out = sum_i exp(lse_i - LSE) * out_i.
+ * Same arithmetic as the reference's split combine (reference:
+ * csrc/bit_decode/src/flash_fwd_kernel.h:1217-1231, 1280-1298), usable on
+ * partials that came from other GPUs: the pointer arrays live in HOST memory
+ * and hold device pointers (local, or peer pointers mapped into this process).
+ */
+#define BD_MAX_PARTS 16
+typedef struct bd_combine_args {
+    int32_t n_parts;                      /* 1 .. BD_MAX_PARTS */
+    const float *const *part_out;         /* host array of n device pointers, each (rows, d) fp32 */
+    const float *const *part_lse;         /* host array of n device pointers, each (rows) fp32 */
+    int64_t rows;                         /* b * h */
+    int32_t d;
+    void *out;                            /* (rows, d) in out_dtype, contiguous */
+    float *lse;                           /* optional (rows) */
+    int32_t out_dtype;
+} bd_combine_args;
+
+int bd_combine(const bd_combine_args *args, bd_stream_t stream);
+
+/*
+ * Blocks until the work queued on `stream` is done and returns the status word
+ * the last bd_decode on that workspace left: BD_OK, or BD_ERR_TIMEOUT if a
+ * bounded wait inside a kernel ran out.  Synchronises; meant for tests and
+ * debugging, not for the hot path.
+ */
+int bd_read_status(const void *workspace, bd_stream_t stream);
+
+const char *bd_strerror(int code);
+int bd_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BITDECODE_H_ */
