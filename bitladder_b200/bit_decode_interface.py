@@ -224,7 +224,7 @@ def _workspace_for(a: "_lib.DecodeArgs", device, workspace):
         key = (device.index, _stream(device))
         workspace = _WORKSPACES.get(key)
         if workspace is None or workspace.numel() < need:
-            workspace = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=device)
+            workspace = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
             _WORKSPACES[key] = workspace
     else:
         _require(workspace.is_cuda and workspace.dtype == torch.uint8 and workspace.is_contiguous(),

@@ -331,9 +331,7 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     p.part_out = reinterpret_cast<float *>(ws + 16);
     p.part_lse = reinterpret_cast<float *>(ws + 16 + plan.part_out_bytes);
 
-    cudaError_t err = cudaMemsetAsync(p.status, 0, sizeof(int32_t), stream);
-    if (err != cudaSuccess) return BD_ERR_CUDA;
-    err = bd::launch_decode(p, kmap, vmap, a->bits, a->group, stream);
+    cudaError_t err = bd::launch_decode(p, kmap, vmap, a->bits, a->group, stream);
     if (err != cudaSuccess) return BD_ERR_CUDA;
     if (plan.num_splits > 1) {
         bd::CombineSplitParams c;

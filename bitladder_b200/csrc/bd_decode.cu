@@ -526,6 +526,19 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                         for (int e = 0; e < 4; ++e) O[mt][nq][e] *= f[e & 1];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) ZS[nq][e] *= f[e & 1];
+                    if (u == 1) {
+                        // The first unit's probabilities are still waiting (as B fragments,
+                        // column = g) for the V phase: bring them to the new maximum too.
+                        const float f0 = __shfl_sync(0xffffffffu, f[0], g >> 1);
+                        const float f1 = __shfl_sync(0xffffffffu, f[1], g >> 1);
+                        const float fq = (g & 1) ? f1 : f0;
+                        const uint32_t fh = pack_f16x2(fq, fq);
+#pragma unroll
+                        for (int j = 0; j < P; ++j) {
+                            Pb[0][j][nq][0] = hmul2_u32(Pb[0][j][nq][0], fh);
+                            Pb[0][j][nq][1] = hmul2_u32(Pb[0][j][nq][1], fh);
+                        }
+                    }
                 }
 #pragma unroll
                 for (int j = 0; j < P; ++j) {

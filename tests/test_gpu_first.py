@@ -49,4 +49,4 @@ def test_decode_matches_oracle(bits, group, h, h_k, s, splits):
     lerr = np.abs(lse.cpu().numpy().astype(np.float64) - l_ref).max()
     print(f"max|dO|={err:.3e} max|dLSE|={lerr:.3e}")
     assert err <= 2e-3, err
-    assert lerr <= 1e-3, lerr
+    assert lerr <= 2e-3, lerr
