@@ -18,6 +18,7 @@ BD_MAX_PARTS = 16
 EXPORTS = (
     "bd_pack", "bd_decode", "bd_decode_workspace_bytes", "bd_plan_splits",
     "bd_combine", "bd_read_status", "bd_strerror", "bd_version",
+    "bd_partition_segments", "bd_partition_parts",
 )
 
 
@@ -97,6 +98,10 @@ def load():
     lib.bd_plan_splits.restype = C.c_int
     lib.bd_combine.argtypes = [C.POINTER(CombineArgs), C.c_void_p]
     lib.bd_combine.restype = C.c_int
+    lib.bd_partition_segments.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
+    lib.bd_partition_segments.restype = C.c_int
+    lib.bd_partition_parts.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
+    lib.bd_partition_parts.restype = C.c_int
     lib.bd_read_status.argtypes = [C.c_void_p, C.c_void_p]
     lib.bd_read_status.restype = C.c_int
     lib.bd_strerror.argtypes = [C.c_int]

@@ -280,11 +280,12 @@ def fwd_kvcache_int(q: torch.Tensor,
 
 
 def decode_workspace_bytes(q, k_pack, k_params, v_pack, v_params, group_size=128, num_bits=4,
-                           seqlen_k=None, num_splits=0) -> int:
-    """Bytes of workspace a decode call with these tensors needs."""
-    out = q
+                           seqlen_k=None, num_splits=0, k_res=None, v_res=None, res_lens=None,
+                           cache_seqlens=None) -> int:
+    """Bytes of workspace a decode call with these tensors needs (the tail and
+    per-sequence lengths add to it, so pass them if the call will)."""
     a = _decode_args(q, k_pack, k_params, v_pack, v_params, 1.0, group_size, num_bits,
-                     None, None, None, None, seqlen_k, out, None, num_splits)
+                     k_res, v_res, res_lens, cache_seqlens, seqlen_k, q, None, num_splits)
     with torch.cuda.device(q.device):
         return int(_lib.load().bd_decode_workspace_bytes(C.byref(a)))
 

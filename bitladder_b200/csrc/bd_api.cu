@@ -88,42 +88,47 @@ bool config_supported(int bits, int group, int d) {
 }
 
 struct DecodePlan {
-    int num_splits;
-    int chunk_blocks;
-    size_t part_out_bytes, part_lse_bytes, total_bytes;
+    int rows;                 // R: ranges the block list of one KV head is cut into
+    bool ragged;
+    size_t off_table, off_part_out, off_part_lse, total_bytes;
 };
+
+inline size_t align16(size_t x) { return (x + 15) & ~size_t(15); }
 
 // Every CTA of the decode grid should be resident at once (one wave) and carry
 // the same number of pack blocks: then all of them stream at the same rate and
-// finish together.  Pick the largest split count whose grid still fits.
-int plan_splits(int b, int h_k, int64_t max_s, int bits, int sm_count, int ctas_per_sm) {
+// finish together.  rows * h_k CTAs fill the resident slots; a row never gets
+// fewer than four blocks (one per warp).
+int plan_rows(int b, int h_k, int64_t max_s, int bits, int sm_count, int ctas_per_sm) {
     if (b <= 0 || h_k <= 0 || max_s <= 0) return 1;
     const int nb = pack_block_tokens(bits);
     const int64_t nblk = (max_s + nb - 1) / nb;
-    if (ctas_per_sm <= 0) ctas_per_sm = bd::decode_ctas_per_sm_default();
+    if (ctas_per_sm <= 0) ctas_per_sm = 3;
     const int64_t slots = int64_t(sm_count) * ctas_per_sm;
-    const int64_t pairs = int64_t(b) * h_k;
-    int64_t splits = std::max<int64_t>(1, slots / pairs);
-    // at least 4 blocks per split (one per consumer warp), at most 128 splits
-    splits = std::min<int64_t>(splits, std::max<int64_t>(1, nblk / 4));
-    splits = std::min<int64_t>(splits, 128);
-    const int64_t chunk = (nblk + splits - 1) / splits;
-    return int((nblk + chunk - 1) / chunk);
+    int64_t rows = std::max<int64_t>(1, slots / h_k);
+    rows = std::min<int64_t>(rows, std::max<int64_t>(1, (int64_t(b) * nblk + 3) / 4));
+    return int(std::min<int64_t>(rows, 1 << 20));
 }
 
 int make_plan(const bd_decode_args *a, int sm_count, DecodePlan &plan) {
     const int nb = pack_block_tokens(a->bits);
-    const int64_t nblk = std::max<int64_t>(1, (int64_t(a->s) + nb - 1) / nb);
-    int splits = a->num_splits > 0 ? a->num_splits : plan_splits(a->b, a->h_k, a->s, a->bits, sm_count, 0);
-    splits = int(std::min<int64_t>(splits, nblk));
-    splits = std::max(1, std::min(splits, 1024));
-    const int64_t chunk = (nblk + splits - 1) / splits;
-    plan.chunk_blocks = int(chunk);
-    plan.num_splits = int((nblk + chunk - 1) / chunk);
-    const size_t rows = size_t(a->b) * a->h;
-    plan.part_out_bytes = plan.num_splits > 1 ? rows * plan.num_splits * 128 * sizeof(float) : 0;
-    plan.part_lse_bytes = plan.num_splits > 1 ? ((rows * plan.num_splits * sizeof(float) + 15) / 16) * 16 : 0;
-    plan.total_bytes = plan.part_out_bytes + plan.part_lse_bytes + 16;
+    const int64_t nblk = (int64_t(a->s) + nb - 1) / nb;
+    const int gq = a->h / a->h_k;
+    int64_t rows;
+    if (a->num_splits > 0) {
+        rows = std::min<int64_t>(int64_t(a->num_splits) * a->b, std::max<int64_t>(1, int64_t(a->b) * nblk));
+    } else {
+        rows = plan_rows(a->b, a->h_k, a->s, a->bits, sm_count, bd::decode_ctas_per_sm(a->bits, a->group, gq));
+    }
+    plan.rows = int(std::max<int64_t>(1, std::min<int64_t>(rows, 1 << 20)));
+    plan.ragged = a->cache_seqlens != nullptr;
+    const size_t slots = (size_t(plan.rows) + a->b) * a->h_k;
+    size_t off = 16;                                  // status word
+    plan.off_table = off;
+    if (plan.ragged) off = align16(off + (size_t(a->b) + 1) * 2 * sizeof(int32_t));
+    plan.off_part_out = off; off += slots * gq * 128 * sizeof(float);
+    plan.off_part_lse = off; off = align16(off + slots * gq * sizeof(float));
+    plan.total_bytes = off;
     return BD_OK;
 }
 
@@ -205,6 +210,34 @@ extern "C" {
 
 int bd_version(void) { return BD_VERSION; }
 
+int bd_partition_segments(const int32_t *table, int b, int n_uniform, int rows, int row, int32_t *out, int max_segments) {
+    if (b <= 0 || rows <= 0 || row < 0 || row >= rows || !out || max_segments < 0) return BD_ERR_INVALID;
+    bd::Partition pt{table, b, n_uniform, rows};
+    bd::SegWalk walk;
+    walk.init(pt, row);
+    bd::Segment sg;
+    int n = 0;
+    while (walk.next(sg)) {
+        if (n < max_segments) {
+            out[4 * n] = sg.ib; out[4 * n + 1] = sg.u0; out[4 * n + 2] = sg.u1; out[4 * n + 3] = sg.owns_tail ? 1 : 0;
+        }
+        ++n;
+    }
+    return n;
+}
+
+int bd_partition_parts(const int32_t *table, int b, int n_uniform, int rows, int ib, int has_tail,
+                       int32_t *out, int max_parts) {
+    if (b <= 0 || rows <= 0 || ib < 0 || ib >= b || !out || max_parts < 0) return BD_ERR_INVALID;
+    bd::Partition pt{table, b, n_uniform, rows};
+    int n = 0;
+    bd::for_each_part(pt, ib, has_tail != 0, [&](int c) {
+        if (n < max_parts) out[n] = c;
+        ++n;
+    });
+    return n;
+}
+
 const char *bd_strerror(int code) {
     switch (code) {
         case BD_OK: return "ok";
@@ -222,7 +255,7 @@ const char *bd_strerror(int code) {
 
 int bd_plan_splits(int b, int h_k, int64_t max_s, int bits, int sm_count, int ctas_per_sm) {
     if (bits != 2 && bits != 4) return 1;
-    return plan_splits(b, h_k, max_s, bits, sm_count, ctas_per_sm);
+    return plan_rows(b, h_k, max_s, bits, sm_count, ctas_per_sm);
 }
 
 int bd_pack(const bd_pack_args *a, bd_stream_t stream) {
@@ -286,7 +319,6 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     make_plan(a, info.sm_count, plan);
     if (!a->workspace || a->workspace_bytes < plan.total_bytes) return BD_ERR_WORKSPACE;
     if (!aligned16(a->workspace)) return BD_ERR_ALIGNMENT;
-    if (a->b > 65535 || plan.num_splits > 65535) return BD_ERR_INVALID;
 
     const int P = 16 / a->bits, nb = 32 * P, dp = 128 / P;
     const int64_t k_row = int64_t(a->h_k) * 128, v_row = int64_t(a->h_k) * dp;
@@ -294,6 +326,7 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     const uint64_t k_rows_total = uint64_t(a->b - 1) * k_batch_rows + uint64_t(a->s_cap / P);
     const uint64_t v_rows_total = uint64_t(a->b - 1) * v_batch_rows + uint64_t(a->s_cap);
     if (k_rows_total > 0x7fffffffull || v_rows_total > 0x7fffffffull) return BD_ERR_INVALID;
+    if (int64_t(plan.rows) * a->h_k > 0x7fffffffll) return BD_ERR_INVALID;
 
     CUtensorMap kmap, vmap;
     rc = get_map(&kmap, a->k_pack, uint64_t(k_row), k_rows_total, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -303,11 +336,26 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     if (rc != BD_OK) return rc;
 
     uint8_t *ws = static_cast<uint8_t *>(a->workspace);
+    bd::Partition part;
+    part.table = plan.ragged ? reinterpret_cast<const int32_t *>(ws + plan.off_table) : nullptr;
+    part.b = a->b;
+    part.n_uniform = int32_t((int64_t(a->s) + nb - 1) / nb);
+    part.R = plan.rows;
+
+    cudaError_t err;
+    if (plan.ragged) {
+        bd::PrefixParams pp;
+        pp.cache_seqlens = a->cache_seqlens;
+        pp.table = reinterpret_cast<int32_t *>(ws + plan.off_table);
+        pp.b = a->b; pp.s = a->s; pp.block_tokens = nb;
+        err = bd::launch_prefix(pp, stream);
+        if (err != cudaSuccess) return BD_ERR_CUDA;
+    }
+
     DecodeParams p;
     std::memset(&p, 0, sizeof(p));
-    p.q = a->q; p.out = a->out; p.lse = a->lse;
+    p.q = a->q;
     p.q_stride_b = a->q_stride_b; p.q_stride_h = a->q_stride_h;
-    p.out_stride_b = a->out_stride_b; p.out_stride_h = a->out_stride_h;
     p.k_params = static_cast<const uint16_t *>(a->k_params);
     p.v_params = static_cast<const uint16_t *>(a->v_params);
     p.k_params_stride_b = 2 * a->k_params_stride_b;
@@ -320,33 +368,30 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     p.res_lens = a->res_lens; p.res_len = a->k_res ? a->res_len : 0;
     p.b = a->b; p.h = a->h; p.h_k = a->h_k; p.gq = a->h / a->h_k;
     p.s = a->s;
-    p.chunk_blocks = plan.chunk_blocks;
-    p.num_splits = plan.num_splits;
     p.k_batch_rows = int32_t(k_batch_rows);
     p.v_batch_rows = int32_t(v_batch_rows);
-    p.dtype = a->dtype; p.out_dtype = a->out_dtype;
+    p.dtype = a->dtype;
     p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
-    // workspace: [status word, 16 B][partial outputs][partial LSEs]
+    p.part = part;
+    // workspace: [status word, 16 B][sequence table][segment partials]
     p.status = reinterpret_cast<int32_t *>(ws);
-    p.part_out = reinterpret_cast<float *>(ws + 16);
-    p.part_lse = reinterpret_cast<float *>(ws + 16 + plan.part_out_bytes);
+    p.part_out = reinterpret_cast<float *>(ws + plan.off_part_out);
+    p.part_lse = reinterpret_cast<float *>(ws + plan.off_part_lse);
 
-    cudaError_t err = bd::launch_decode(p, kmap, vmap, a->bits, a->group, stream);
+    err = bd::launch_decode(p, kmap, vmap, a->bits, a->group, stream);
     if (err != cudaSuccess) return BD_ERR_CUDA;
-    if (plan.num_splits > 1) {
-        bd::CombineSplitParams c;
-        std::memset(&c, 0, sizeof(c));
-        c.part_out = p.part_out; c.part_lse = p.part_lse;
-        c.out = a->out; c.lse = a->lse;
-        c.out_stride_b = a->out_stride_b; c.out_stride_h = a->out_stride_h;
-        c.cache_seqlens = a->cache_seqlens;
-        c.b = a->b; c.h = a->h; c.s = a->s;
-        c.num_splits = plan.num_splits;
-        c.chunk_tokens = plan.chunk_blocks * nb;
-        c.out_dtype = a->out_dtype;
-        err = bd::launch_combine_splits(c, stream);
-        if (err != cudaSuccess) return BD_ERR_CUDA;
-    }
+
+    bd::CombineParams c;
+    std::memset(&c, 0, sizeof(c));
+    c.part_out = p.part_out; c.part_lse = p.part_lse;
+    c.out = a->out; c.lse = a->lse;
+    c.out_stride_b = a->out_stride_b; c.out_stride_h = a->out_stride_h;
+    c.res_lens = a->res_lens; c.res_len = p.res_len; c.has_tail = a->k_res != nullptr;
+    c.b = a->b; c.h = a->h; c.h_k = a->h_k; c.gq = p.gq;
+    c.out_dtype = a->out_dtype;
+    c.part = part;
+    err = bd::launch_combine(c, stream);
+    if (err != cudaSuccess) return BD_ERR_CUDA;
     return BD_OK;
 }
 

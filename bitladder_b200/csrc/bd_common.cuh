@@ -105,7 +105,7 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t &r0, uint3
 }
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
     uint32_t d;
-    asm("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
     return d;
 }
 __device__ __forceinline__ void lds128(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {

@@ -1,12 +1,16 @@
-// Internal parameter blocks and launch prototypes shared by the kernel
-// translation units and the C-ABI layer.  Plain structs passed by value to
-// the kernels (the reference passes one large Flash_fwd_params for everything,
+// Internal parameter blocks, the work partition shared by the decode and the
+// combine kernels, and launch prototypes.  Plain structs passed by value to the
+// kernels (the reference passes one large Flash_fwd_params for everything,
 // reference: csrc/bit_decode/src/include/flash.h:24-198).
 #pragma once
 
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#ifndef BD_HD
+#define BD_HD __host__ __device__ __forceinline__
+#endif
 
 namespace bd {
 
@@ -23,11 +27,114 @@ struct PackParams {
     int32_t dst_token_offset;
 };
 
+// ---------------------------------------------------------------------------
+// Work partition of one decode step.
+//
+// Per KV head, the pack blocks of all sequences form one flat list of T units
+// (sequence 0's blocks, then sequence 1's, ...).  The list is cut into R equal
+// ranges ("rows"); CTA (row c, head ih) streams range c of head ih, so all CTAs
+// carry the same number of blocks (+-1) whatever the batch size and however
+// ragged the lengths are, and the CTAs of one row touch the same tokens of
+// neighbouring heads at the same time.  A range that crosses a sequence boundary
+// yields one partial result per sequence it touches ("segment"); the segment of
+// (row c, sequence ib) owns partial slot c + ib, which is unique because rows and
+// sequences both advance monotonically along the list.  The unquantized tail of a
+// sequence is streamed by the row in which the sequence starts (the last row for
+// empty sequences at the very end) and lands in that row's partial.  The combine
+// kernel walks the same arithmetic to find the parts.
+// ---------------------------------------------------------------------------
+struct Partition {
+    const int32_t *table;     // ragged: (first unit, unit count) per sequence, then (T, 0); null when uniform
+    int32_t b;
+    int32_t n_uniform;        // units per sequence when table is null
+    int32_t R;                // rows
+
+    BD_HD int64_t total() const { return table ? int64_t(table[2 * b]) : int64_t(b) * n_uniform; }
+    BD_HD int64_t first(int ib) const { return table ? int64_t(table[2 * ib]) : int64_t(ib) * n_uniform; }
+    BD_HD int32_t count(int ib) const { return table ? table[2 * ib + 1] : n_uniform; }
+    // first unit of row c (c == R gives T)
+    BD_HD int64_t row_begin(int c, int64_t T) const { return (int64_t(c) * T) / R; }
+    // row that holds unit f (0 <= f < T)
+    BD_HD int32_t row_of(int64_t f, int64_t T) const { return int32_t(((f + 1) * R - 1) / T); }
+};
+
+// One segment of a row: units [u0, u1) of sequence ib (u1 <= u0: no pack blocks,
+// the row only owns the sequence's tail).
+struct Segment {
+    int32_t ib, u0, u1;
+    bool owns_tail;
+};
+
+// Walks the segments of row c in order.  Pure integer arithmetic on the
+// partition, shared by the decode kernel and by host-side tests.
+struct SegWalk {
+    const Partition *ptp;
+    int64_t T, f0, f1;
+    int32_t c, ib;
+
+    BD_HD void init(const Partition &p, int row) {
+        ptp = &p;
+        c = row;
+        T = p.total();
+        f0 = p.row_begin(row, T);
+        f1 = p.row_begin(row + 1, T);
+        ib = find_start();
+    }
+    // smallest ib with first(ib) >= f0 or first(ib) + count(ib) > f0
+    BD_HD int32_t find_start() const {
+        const Partition &pt = *ptp;
+        if (!pt.table) return pt.n_uniform > 0 ? int32_t(f0 / pt.n_uniform) : 0;
+        int32_t lo = 0, hi = pt.b;
+        while (lo < hi) {
+            const int32_t mid = (lo + hi) >> 1;
+            const bool ok = pt.first(mid) + pt.count(mid) > f0 || pt.first(mid) >= f0;
+            if (ok) hi = mid; else lo = mid + 1;
+        }
+        return lo;
+    }
+    BD_HD bool next(Segment &sg) {
+        const Partition &pt = *ptp;
+        while (ib < pt.b) {
+            const int64_t fb = pt.first(ib);
+            const bool trailing = (c == pt.R - 1) && fb >= T;      // empty sequences after the last unit
+            if (fb >= f1 && !trailing) break;
+            const int64_t n = pt.count(ib);
+            const int64_t lo = fb > f0 ? fb : f0;
+            const int64_t hi = fb + n < f1 ? fb + n : f1;
+            sg.ib = ib;
+            sg.u0 = int32_t(lo - fb);
+            sg.u1 = int32_t(hi - fb);
+            sg.owns_tail = trailing || (fb >= f0 && fb < f1);
+            ++ib;
+            if (sg.u1 > sg.u0 || sg.owns_tail) return true;
+        }
+        return false;
+    }
+};
+
+// Rows that hold a part of sequence ib (the combine side of the same arithmetic):
+// calls f(c) for every row c whose range overlaps the sequence's units.  A
+// sequence without pack blocks but with a tail has one part, in the row that
+// owns its tail.
+template <class F>
+BD_HD void for_each_part(const Partition &pt, int ib, bool has_tail, F &&f) {
+    const int64_t T = pt.total();
+    const int64_t first = pt.first(ib), n = pt.count(ib);
+    if (n > 0 && T > 0) {
+        const int c0 = pt.row_of(first, T), c1 = pt.row_of(first + n - 1, T);
+        for (int c = c0; c <= c1; ++c) {
+            const int64_t b0 = pt.row_begin(c, T), b1 = pt.row_begin(c + 1, T);
+            const int64_t lo = b0 > first ? b0 : first, hi = b1 < first + n ? b1 : first + n;
+            if (hi > lo) f(c);                 // rows without blocks exist when there are more rows than units
+        }
+    } else if (has_tail) {
+        f(T > 0 ? pt.row_of(first < T ? first : T - 1, T) : pt.R - 1);
+    }
+}
+
 struct DecodeParams {
     const void *q;
-    void *out;
-    float *lse;
-    int64_t q_stride_b, q_stride_h, out_stride_b, out_stride_h;
+    int64_t q_stride_b, q_stride_h;
     const uint16_t *k_params;     // viewed as fp16
     const uint16_t *v_params;
     int64_t k_params_stride_b;    // in fp16 elements
@@ -39,25 +146,33 @@ struct DecodeParams {
     int32_t res_len;
     int32_t b, h, h_k, gq;
     int32_t s;
-    int32_t chunk_blocks;         // pack blocks per split
-    int32_t num_splits;
     int32_t k_batch_rows;         // K batch stride in pack rows
     int32_t v_batch_rows;         // V batch stride in token rows
-    int32_t dtype, out_dtype;
+    int32_t dtype;
     float scale_log2;             // softmax_scale * log2(e)
-    float *part_out;              // (b*h, num_splits, d) fp32
-    float *part_lse;              // (b*h, num_splits) fp32
+    Partition part;
+    float *part_out;              // [(R + b) * h_k segment slots][gq][128] fp32, normalised
+    float *part_lse;              // [(R + b) * h_k][gq]
     int32_t *status;
 };
 
-struct CombineSplitParams {
+struct CombineParams {
     const float *part_out, *part_lse;
     void *out;
     float *lse;
     int64_t out_stride_b, out_stride_h;
-    const int32_t *cache_seqlens;
-    int32_t b, h, s, num_splits, chunk_tokens;
+    const int32_t *res_lens;      // per-sequence tail lengths, or null
+    int32_t res_len;              // tail length when res_lens is null (0: no tail)
+    int32_t has_tail;             // a tail buffer was given
+    int32_t b, h, h_k, gq;
     int32_t out_dtype;
+    Partition part;
+};
+
+struct PrefixParams {
+    const int32_t *cache_seqlens;
+    int32_t *table;
+    int32_t b, s, block_tokens;
 };
 
 struct CombinePartsParams {
@@ -71,11 +186,11 @@ struct CombinePartsParams {
 };
 
 cudaError_t launch_pack(const PackParams &p, int bits, int group, int dtype, cudaStream_t stream);
+cudaError_t launch_prefix(const PrefixParams &p, cudaStream_t stream);
 cudaError_t launch_decode(const DecodeParams &p, const CUtensorMap &kmap, const CUtensorMap &vmap,
                           int bits, int group, cudaStream_t stream);
-size_t decode_smem_bytes(int bits, int group, int gq);
-int decode_ctas_per_sm_default();
-cudaError_t launch_combine_splits(const CombineSplitParams &p, cudaStream_t stream);
+int decode_ctas_per_sm(int bits, int group, int gq);
+cudaError_t launch_combine(const CombineParams &p, cudaStream_t stream);
 cudaError_t launch_combine_parts(const CombinePartsParams &p, cudaStream_t stream);
 
 }  // namespace bd

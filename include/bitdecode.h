@@ -101,7 +101,8 @@ int bd_pack(const bd_pack_args *args, bd_stream_t stream);
  * tail, nor per-sequence lengths, nor a returned LSE; they are extensions.
  *
  * The workspace (bd_decode_workspace_bytes) starts with one status word (16
- * bytes reserved) followed by the per-split partial results.  The caller zeroes
+ * bytes reserved) followed by the per-sequence block table (ragged batches) and
+ * the partial results of every range.  The caller zeroes
  * the first 16 bytes once after allocating it; bd_decode only ever writes a
  * non-zero error code there (BD_ERR_TIMEOUT), so the hot path has no memset.
  * The same workspace must not be used by two decode calls that can overlap on
@@ -129,7 +130,7 @@ typedef struct bd_decode_args {
     int32_t dtype;            /* of q and the tail: BD_FP16 / BD_BF16 */
     int32_t out_dtype;        /* BD_FP16 / BD_BF16 / BD_FP32 */
     float softmax_scale;
-    int32_t num_splits;       /* 0 = choose (bd_plan_splits) */
+    int32_t num_splits;       /* 0 = choose (bd_plan_splits); n > 0 = about n ranges per sequence */
     void *workspace;
     size_t workspace_bytes;
 } bd_decode_args;
@@ -140,11 +141,31 @@ int bd_decode(const bd_decode_args *args, bd_stream_t stream);
 size_t bd_decode_workspace_bytes(const bd_decode_args *args);
 
 /*
- * Number of sequence splits bd_decode uses when num_splits == 0; replaces
- * num_splits_heuristic (reference: csrc/bit_decode/decode_api.cpp:234-268).
- * `ctas_per_sm` <= 0 selects the library default.
+ * How bd_decode splits the sequence dimension when num_splits == 0; takes the
+ * place of num_splits_heuristic (reference: csrc/bit_decode/decode_api.cpp:234-268).
+ * Per KV head the pack blocks of all sequences form one list; the list is cut
+ * into this many equal ranges ("rows"), one CTA per (row, KV head), so the grid
+ * fills every SM with `ctas_per_sm` resident CTAs of equal work whatever the
+ * batch size and lengths.  A caller-given num_splits > 0 asks for
+ * num_splits * b rows instead.  `ctas_per_sm` <= 0 selects the default (3).
  */
 int bd_plan_splits(int b, int h_k, int64_t max_s, int bits, int sm_count, int ctas_per_sm);
+
+/*
+ * Host-side view of that partition, for tests and debugging (pure integer
+ * arithmetic, no device work, no counterpart in the reference).  `table` is null
+ * for equal lengths (then every sequence has n_uniform pack blocks) or points
+ * to HOST memory holding (first block, block count) per sequence followed by
+ * (total, 0).  bd_partition_segments writes up to max_segments tuples
+ * (sequence, first block, end block, owns_tail) covered by `row`;
+ * bd_partition_parts writes the rows that hold a part of sequence `ib`
+ * (`has_tail`: the sequence has unquantized tail tokens).
+ * Both return the number of entries found.
+ */
+int bd_partition_segments(const int32_t *table, int b, int n_uniform, int rows, int row,
+                          int32_t *out, int max_segments);
+int bd_partition_parts(const int32_t *table, int b, int n_uniform, int rows, int ib, int has_tail,
+                       int32_t *out, int max_parts);
 
 /*
  * Merge n partial results (each normalised within its part) with their
