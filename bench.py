@@ -432,11 +432,11 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "peak_source": peak_src,
                          "note": "achieved = algorithmic bytes per step / CUDA-event time of the whole step "
-                                 "(split-KV decode kernel + split combine launched back to back)",
+                                 "(one split-KV decode kernel launch; the range that finishes last merges the partials)",
                          "algorithmic_bytes_per_step": nbytes},
             "cpu_baseline": cpu,
             "e2e": e2e,
-            "gpu_launches": (3 if w["ragged"] else 2) * steps,
+            "gpu_launches": (2 if w["ragged"] else 1) * steps,
             "clocks": clocks,
             "pack_gb_s": pack_gbs,
         }

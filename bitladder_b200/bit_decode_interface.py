@@ -221,11 +221,19 @@ def _workspace_for(a: "_lib.DecodeArgs", device, workspace):
     need = int(_lib.load().bd_decode_workspace_bytes(C.byref(a)))
     _require(need > 0, "bd_decode_workspace_bytes rejected the arguments")
     if workspace is None:
+        # Cached per (device, stream).  The library wants a zeroed workspace and leaves
+        # its counters at zero after every call, but their place depends on the batch
+        # size and head count: clear the buffer again whenever that layout changes.
         key = (device.index, _stream(device))
-        workspace = _WORKSPACES.get(key)
-        if workspace is None or workspace.numel() < need:
-            workspace = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
-            _WORKSPACES[key] = workspace
+        layout = (a.b, a.h_k, a.cache_seqlens is not None)
+        entry = _WORKSPACES.get(key)
+        if entry is None or entry[0].numel() < need:
+            entry = [torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device), layout]
+            _WORKSPACES[key] = entry
+        elif entry[1] != layout:
+            entry[0].zero_()
+            entry[1] = layout
+        workspace = entry[0]
     else:
         _require(workspace.is_cuda and workspace.dtype == torch.uint8 and workspace.is_contiguous(),
                  "workspace must be a contiguous uint8 CUDA tensor")
@@ -259,7 +267,9 @@ def fwd_kvcache_int(q: torch.Tensor,
     buffers' capacity, like the reference's ``v_pack.size(1)``); ``return_lse``
     also returns the (b, h) fp32 log-sum-exp of the scaled scores; ``out`` /
     ``out_dtype`` (fp16, bf16 or fp32) / ``workspace`` / ``num_splits`` for callers
-    that manage memory and scheduling themselves.  Asynchronous on the current stream.
+    that manage memory and scheduling themselves (a caller-provided ``workspace`` must
+    be zero-filled once, and again whenever the batch size or KV head count it is used
+    with changes).  Asynchronous on the current stream.
     """
     _check_config(quant_mode, group_size, num_bits)
     _require(opt_block_table is None, "paged KV caches (opt_block_table) are not supported")

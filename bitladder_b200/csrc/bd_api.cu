@@ -90,7 +90,7 @@ bool config_supported(int bits, int group, int d) {
 struct DecodePlan {
     int rows;                 // R: ranges the block list of one KV head is cut into
     bool ragged;
-    size_t off_table, off_part_out, off_part_lse, total_bytes;
+    size_t off_counters, off_table, off_part_out, off_part_lse, total_bytes;
 };
 
 inline size_t align16(size_t x) { return (x + 15) & ~size_t(15); }
@@ -124,6 +124,8 @@ int make_plan(const bd_decode_args *a, int sm_count, DecodePlan &plan) {
     plan.ragged = a->cache_seqlens != nullptr;
     const size_t slots = (size_t(plan.rows) + a->b) * a->h_k;
     size_t off = 16;                                  // status word
+    plan.off_counters = off;
+    off = align16(off + size_t(a->b) * a->h_k * sizeof(int32_t));
     plan.off_table = off;
     if (plan.ragged) off = align16(off + (size_t(a->b) + 1) * 2 * sizeof(int32_t));
     plan.off_part_out = off; off += slots * gq * 128 * sizeof(float);
@@ -373,7 +375,11 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     p.dtype = a->dtype;
     p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
     p.part = part;
-    // workspace: [status word, 16 B][sequence table][segment partials]
+    // workspace: [status word, 16 B][arrival counters][sequence table][segment partials]
+    p.counters = reinterpret_cast<int32_t *>(ws + plan.off_counters);
+    p.out = a->out; p.lse = a->lse;
+    p.out_stride_b = a->out_stride_b; p.out_stride_h = a->out_stride_h;
+    p.out_dtype = a->out_dtype;
     p.status = reinterpret_cast<int32_t *>(ws);
     p.part_out = reinterpret_cast<float *>(ws + plan.off_part_out);
     p.part_lse = reinterpret_cast<float *>(ws + plan.off_part_lse);
@@ -381,17 +387,6 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     err = bd::launch_decode(p, kmap, vmap, a->bits, a->group, stream);
     if (err != cudaSuccess) return BD_ERR_CUDA;
 
-    bd::CombineParams c;
-    std::memset(&c, 0, sizeof(c));
-    c.part_out = p.part_out; c.part_lse = p.part_lse;
-    c.out = a->out; c.lse = a->lse;
-    c.out_stride_b = a->out_stride_b; c.out_stride_h = a->out_stride_h;
-    c.res_lens = a->res_lens; c.res_len = p.res_len; c.has_tail = a->k_res != nullptr;
-    c.b = a->b; c.h = a->h; c.h_k = a->h_k; c.gq = p.gq;
-    c.out_dtype = a->out_dtype;
-    c.part = part;
-    err = bd::launch_combine(c, stream);
-    if (err != cudaSuccess) return BD_ERR_CUDA;
     return BD_OK;
 }
 

@@ -7,11 +7,11 @@
 // the weighted sum).  One warp per (batch, query head) row, each lane owns four
 // consecutive head dims (one 16-byte load per partial).
 //
-// Two variants: the step combine finds the partials bd_decode left in its
-// workspace by walking the same work partition as the decode kernel (one part
-// per row that streamed blocks, or the tail, of the sequence); the
-// parts combine takes one pointer per part, which may point into another GPU's
-// memory (plain loads over NVLink, no multicast, no TMA).
+// Inside one decode step the merge of the per-range partials is done by the
+// decode kernel itself (the range that finishes last merges); this file holds
+// the stand-alone variant that takes one pointer per part, for partial results
+// that come from other GPUs: the pointers may point into a peer's memory (plain
+// loads over NVLink, no multicast, no TMA).
 #include "bd_common.cuh"
 #include "bd_kernels.h"
 
@@ -31,44 +31,6 @@ __device__ __forceinline__ void store_out4(void *out, int64_t idx, const float (
     } else {
         *reinterpret_cast<float4 *>(static_cast<float *>(out) + idx) = make_float4(o[0], o[1], o[2], o[3]);
     }
-}
-
-__global__ void __launch_bounds__(kCombineWarps * 32)
-bd_combine_kernel(const CombineParams p) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t row = int64_t(blockIdx.x) * kCombineWarps + warp;
-    if (row >= int64_t(p.b) * p.h) return;
-    const int ib = int(row / p.h), hq = int(row % p.h);
-    const int ih = hq / p.gq, qrow = hq % p.gq;
-
-    const Partition &pt = p.part;
-    bool has_tail = false;
-    if (p.has_tail) has_tail = (p.res_lens ? p.res_lens[ib] : p.res_len) > 0;
-
-    // pass 1: maximum LSE over the parts
-    float mx = -INFINITY;
-    for_each_part(pt, ib, has_tail, [&](int c) {
-        const int64_t slot = (int64_t(c) + ib) * p.h_k + ih;
-        mx = fmaxf(mx, p.part_lse[slot * p.gq + qrow]);
-    });
-    float o[4] = {0.f, 0.f, 0.f, 0.f};
-    float lse = -INFINITY;
-    if (mx != -INFINITY) {
-        float sum = 0.f;
-        for_each_part(pt, ib, has_tail, [&](int c) {
-            const int64_t slot = (int64_t(c) + ib) * p.h_k + ih;
-            const float w = __expf(p.part_lse[slot * p.gq + qrow] - mx);
-            const float4 v = *reinterpret_cast<const float4 *>(p.part_out + (slot * p.gq + qrow) * kHeadDim + 4 * lane);
-            sum += w;
-            o[0] = fmaf(w, v.x, o[0]); o[1] = fmaf(w, v.y, o[1]);
-            o[2] = fmaf(w, v.z, o[2]); o[3] = fmaf(w, v.w, o[3]);
-        });
-        const float inv = 1.0f / sum;
-        o[0] *= inv; o[1] *= inv; o[2] *= inv; o[3] *= inv;
-        lse = mx + logf(sum);
-    }
-    store_out4(p.out, ib * p.out_stride_b + int64_t(hq) * p.out_stride_h + 4 * lane, o, p.out_dtype);
-    if (lane == 0 && p.lse) p.lse[row] = lse;
 }
 
 __global__ void __launch_bounds__(kCombineWarps * 32)
@@ -103,13 +65,6 @@ bd_combine_parts_kernel(const CombinePartsParams p) {
     }
     store_out4(p.out, row * kHeadDim + 4 * lane, o, p.out_dtype);
     if (lane == 0 && p.lse) p.lse[row] = lse;
-}
-
-cudaError_t launch_combine(const CombineParams &p, cudaStream_t stream) {
-    const int64_t rows = int64_t(p.b) * p.h;
-    const unsigned grid = unsigned((rows + kCombineWarps - 1) / kCombineWarps);
-    bd_combine_kernel<<<grid, kCombineWarps * 32, 0, stream>>>(p);
-    return cudaGetLastError();
 }
 
 cudaError_t launch_combine_parts(const CombinePartsParams &p, cudaStream_t stream) {

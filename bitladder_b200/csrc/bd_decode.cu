@@ -62,13 +62,14 @@ struct Cfg {
     static constexpr int DP = kHeadDim / P;             // 16-bit words per V row
     static constexpr int RUNS = NB / 128;               // 128-token runs per block (V params)
     static constexpr int PRM_BYTES = 512 * NGK;         // == NGD * RUNS * 512
-    static constexpr int CODE_BYTES = 8192;
+    static constexpr int CODE_BYTES = 8192;             // one K tile (32 pack rows) or one V tile (NB tokens)
     static constexpr int QROWS = NQT * 8;
     static constexpr int NACC = 8 * NQT * 4 + 4 * NQT;  // floats per thread handed over in a merge
+    // per warp: one K tile and one V tile, then their scales/zeros
     static constexpr size_t OFF_PRM = size_t(kWarps) * 2 * CODE_BYTES;
     static constexpr size_t OFF_XCHG = OFF_PRM + size_t(kWarps) * 2 * PRM_BYTES;
     static constexpr size_t OFF_BAR = OFF_XCHG + size_t(NACC) * 32 * 4;
-    static constexpr size_t SMEM = OFF_BAR + 2 * kWarps * 8 + 16 + 1024;   // + alignment slack
+    static constexpr size_t SMEM = OFF_BAR + 2 * kWarps * 8 + 16;
     static constexpr int CTAS_PER_SM = (SMEM + 1024) * 3 <= 233472 ? 3 : 2;
 };
 
@@ -115,11 +116,15 @@ __device__ __forceinline__ void bar_arrive(int id, int count) {
     asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
-// One online-softmax step for NT score tiles (m16n8 accumulators holding scores in
-// log2 units, columns = query rows): lazily moves the running maxima, rescales
-// the accumulators when a maximum moved, returns the probabilities in t.
-// Returns true when a rescale happened (f holds the factors per column parity).
-template <int NT>
+// One online-softmax step for NT score tiles (m16n8 accumulators, columns = query
+// rows).  On entry t holds the scores in log2 units MINUS the running maximum of
+// their column (minus 0 while the column has no maximum yet); on exit it holds
+// the probabilities.  The running max moves lazily: only when it is exceeded by
+// more than 2^kRescaleSlack, so probabilities stay below 2^8 and the accumulators
+// are rescaled a handful of times per sequence.  With ACC_L the probabilities are
+// also added to l_run (otherwise the caller gets the row sums elsewhere).
+// Returns true when a rescale happened (f holds the factor per column parity).
+template <int NT, bool ACC_L>
 __device__ __forceinline__ bool softmax_step(float (&t)[NT][4], float (&m_run)[2], float (&l_run)[2],
                                              float (&O)[8][4], float (&ZS)[4], float (&f)[2]) {
     float cmax[2] = {-INFINITY, -INFINITY};
@@ -133,20 +138,21 @@ __device__ __forceinline__ bool softmax_step(float (&t)[NT][4], float (&m_run)[2
         cmax[c] = fmaxf(cmax[c], __shfl_xor_sync(0xffffffffu, cmax[c], 8));
         cmax[c] = fmaxf(cmax[c], __shfl_xor_sync(0xffffffffu, cmax[c], 16));
     }
-    // Lazy rescale: the running max only moves when it is exceeded by more than
-    // 2^kRescaleSlack, so probabilities stay below 2^8 and the accumulators are
-    // rescaled a handful of times per sequence.
     bool changed = false;
 #pragma unroll
-    for (int c = 0; c < 2; ++c) changed |= cmax[c] > m_run[c] + kRescaleSlack;
+    for (int c = 0; c < 2; ++c)
+        changed |= cmax[c] > kRescaleSlack || (m_run[c] == -INFINITY && cmax[c] != -INFINITY);
     const bool any = __any_sync(0xffffffffu, changed);
     if (any) {
+        float shift[2];
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-            const float mnew = (cmax[c] > m_run[c] + kRescaleSlack) ? cmax[c] : m_run[c];
-            f[c] = (mnew == -INFINITY) ? 1.f : ex2f(m_run[c] - mnew);
+            const bool first = m_run[c] == -INFINITY;
+            const bool move = cmax[c] > kRescaleSlack || (first && cmax[c] != -INFINITY);
+            shift[c] = move ? cmax[c] : 0.f;
+            f[c] = move ? (first ? 0.f : ex2f(-cmax[c])) : 1.f;
+            if (move) m_run[c] = (first ? 0.f : m_run[c]) + cmax[c];
             l_run[c] *= f[c];
-            m_run[c] = mnew;
         }
 #pragma unroll
         for (int mt = 0; mt < 8; ++mt)
@@ -154,14 +160,17 @@ __device__ __forceinline__ bool softmax_step(float (&t)[NT][4], float (&m_run)[2
             for (int e = 0; e < 4; ++e) O[mt][e] *= f[e & 1];
 #pragma unroll
         for (int e = 0; e < 4; ++e) ZS[e] *= f[e & 1];
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) t[j][e] -= shift[e & 1];
     }
-    const float ms[2] = {m_run[0] == -INFINITY ? 0.f : m_run[0], m_run[1] == -INFINITY ? 0.f : m_run[1]};
 #pragma unroll
     for (int j = 0; j < NT; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            t[j][e] = ex2f(t[j][e] - ms[e & 1]);
-            l_run[e & 1] += t[j][e];
+            t[j][e] = ex2f(t[j][e]);
+            if (ACC_L) l_run[e & 1] += t[j][e];
         }
     return any;
 }
@@ -222,8 +231,9 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     constexpr int DP = C::DP, RUNS = C::RUNS, PRM = C::PRM_BYTES, NACC = C::NACC;
     constexpr int SHIFT = (BITS == 4) ? 8 : 10;
 
-    extern __shared__ uint8_t smem_unaligned[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+    // The swizzled TMA tiles need a 1024-byte aligned base; dynamic shared memory
+    // starts at the beginning of the CTA's window, which is, and the kernel checks it.
+    extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t smem_base = smem_u32(smem);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + C::OFF_BAR + 2 * kWarps * 8);
     float *xchg = reinterpret_cast<float *>(smem + C::OFF_XCHG);
@@ -231,6 +241,10 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int ih = blockIdx.x % p.h_k, row = blockIdx.x / p.h_k;
     const int g = lane >> 2, l = lane & 3;
+    if ((smem_base & 1023u) != 0) {                      // never seen; refuse rather than read garbage
+        if (tid == 0) atomicExch(p.status, BD_ERR_ALIGNMENT);
+        return;
+    }
 
     // this warp's slots and barriers
     const uint32_t kcode = smem_base + (warp * 2) * C::CODE_BYTES;
@@ -302,7 +316,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     for (int j = 0; j < P; ++j) mjs[j] = p.scale_log2 * (1.0f / field_weight<BITS>(j));
 
     const bool bf16 = p.dtype == BD_BF16;
-    uint32_t phase = 0;    // parity of both barriers: one completion per consumed block
+    uint32_t phase = 0;    // parity of both barriers: one completion each per consumed block
     bool aborted = false;
 
     SegWalk walk;
@@ -387,10 +401,11 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const bool ok = (e < 2) ? okA : okB;
-                    S1[nq][0][e] = ok ? S1[nq][0][e] * p.scale_log2 : -INFINITY;
+                    const float mu = m_run[nq][e & 1] == -INFINITY ? 0.f : m_run[nq][e & 1];
+                    S1[nq][0][e] = ok ? fmaf(S1[nq][0][e], p.scale_log2, -mu) : -INFINITY;
                 }
                 float f[2];
-                softmax_step<1>(S1[nq], m_run[nq], l_run[nq], O[nq], ZS[nq], f);
+                softmax_step<1, true>(S1[nq], m_run[nq], l_run[nq], O[nq], ZS[nq], f);
                 pb[nq][0] = movmatrix_trans(pack_f16x2(S1[nq][0][0], S1[nq][0][1]));
                 pb[nq][1] = movmatrix_trans(pack_f16x2(S1[nq][0][2], S1[nq][0][3]));
             }
@@ -518,10 +533,16 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
                 for (int nq = 0; nq < NQT; ++nq) {
                     float t[P][4];
+                    float zm[NGK][2];       // q.zero term minus the running max of the column
+#pragma unroll
+                    for (int gk = 0; gk < NGK; ++gk)
+#pragma unroll
+                        for (int c = 0; c < 2; ++c)
+                            zm[gk][c] = Zc[gk][nq][c] - (m_run[nq][c] == -INFINITY ? 0.f : m_run[nq][c]);
 #pragma unroll
                     for (int j = 0; j < P; ++j)
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) t[j][e] = fmaf(S[j][nq][e], mjs[j], Zc[j / FPG][nq][e & 1]);
+                        for (int e = 0; e < 4; ++e) t[j][e] = fmaf(S[j][nq][e], mjs[j], zm[j / FPG][e & 1]);
                     if (need_mask) {
 #pragma unroll
                         for (int j = 0; j < P; ++j)
@@ -532,7 +553,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                             }
                     }
                     float f[2];
-                    if (softmax_step<P>(t, m_run[nq], l_run[nq], O[nq], ZS[nq], f) && u == 1) {
+                    if (softmax_step<P, (NGD > 1)>(t, m_run[nq], l_run[nq], O[nq], ZS[nq], f) && u == 1) {
                         // The first unit's probabilities are still waiting (as B fragments,
                         // column = g) for the V phase: bring them to the new maximum too.
                         const float f0 = __shfl_sync(0xffffffffu, f[0], g >> 1);
@@ -552,7 +573,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                     }
                 }
             }
-            // K slot consumed: refill it with the next block's K while V is processed
+            // K tile consumed: refill it with the next block's K while V is processed
             __syncwarp();
             if (lane == 0 && ld.valid) {
                 fence_proxy_async();
@@ -587,8 +608,12 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                     uint32_t pv[NGD][NQT][2];
 #pragma unroll
                     for (int nq = 0; nq < NQT; ++nq) {
-                        // sum_t p_t * zero_t  (rows 0-7: dim group 0, rows 8-15: dim group 1)
-                        mma_f16(ZS[nq], ze0[0], ze0[NGD - 1], ze1[0], ze1[NGD - 1], Pb[u][j][nq][0], Pb[u][j][nq][1]);
+                        // rows 0-7: sum_t p_t * zero_t of dim group 0; rows 8-15: the same for dim
+                        // group 1 or, with a single dim group, sum_t p_t (the softmax denominator,
+                        // from the same rounded probabilities the numerator uses)
+                        constexpr uint32_t kOnes = 0x3c003c00u;
+                        mma_f16(ZS[nq], ze0[0], NGD > 1 ? ze0[NGD - 1] : kOnes, ze1[0], NGD > 1 ? ze1[NGD - 1] : kOnes,
+                                Pb[u][j][nq][0], Pb[u][j][nq][1]);
 #pragma unroll
                         for (int gd = 0; gd < NGD; ++gd) {
                             pv[gd][nq][0] = hmul2_u32(Pb[u][j][nq][0], sc0[gd]);
@@ -624,7 +649,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                     }
                 }
             }
-            // V slot consumed: refill it, then move the load cursor on
+            // V tile consumed: refill it, then move the load cursor on
             __syncwarp();
             if (ld.valid) {
                 if (lane == 0) {
@@ -655,10 +680,11 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             }
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                float sum = l_run[nq][c];
+                float sum = l_run[nq][c];           // tail probabilities (and all of them with two dim groups)
                 sum += __shfl_xor_sync(0xffffffffu, sum, 4);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 8);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+                if (NGD == 1) sum += ZS[nq][2 + c];  // every row of the ones block holds the column sum
                 acc[32 * NQT + nq * 4 + c] = m_run[nq][c];
                 acc[32 * NQT + nq * 4 + 2 + c] = sum;
             }
@@ -709,7 +735,17 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             bar_sync(3, 64);
             merge_in();
             bar_arrive(4, 64);
-            // normalise and write this segment's partial: slot (row + ib) of head ih
+            // How many rows hold a part of this sequence?  One: this is the final result.
+            // More: leave a normalised partial; the row that arrives last merges them all.
+            bool seq_tail = false;
+            if (p.k_res != nullptr) seq_tail = (p.res_lens ? p.res_lens[ib] : p.res_len) > 0;
+            const PartRange pr = part_range(p.part, ib, seq_tail);
+            int nparts = pr.c1 - pr.c0 + 1;
+            if (!pr.dense) {
+                nparts = 0;
+                for (int c = pr.c0; c <= pr.c1; ++c) nparts += row_has_part(p.part, ib, c) ? 1 : 0;
+            }
+            const bool final_here = nparts <= 1;
             const int64_t slot = (int64_t(row) + ib) * p.h_k + ih;
 #pragma unroll
             for (int nq = 0; nq < NQT; ++nq) {
@@ -720,7 +756,10 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                     inv[c] = (L > 0.f) ? 1.0f / L : 0.f;
                     lse[c] = (L > 0.f) ? fmaf(M, 0.6931471805599453f, logf(L)) : -INFINITY;
                     const int qrow = nq * 8 + 2 * l + c;
-                    if (g == 0 && qrow < p.gq) p.part_lse[slot * p.gq + qrow] = lse[c];
+                    if (g == 0 && qrow < p.gq) {
+                        if (!final_here) p.part_lse[slot * p.gq + qrow] = lse[c];
+                        else if (p.lse) p.lse[int64_t(ib) * p.h + int64_t(ih) * p.gq + qrow] = lse[c];
+                    }
                 }
 #pragma unroll
                 for (int mt = 0; mt < 8; ++mt) {
@@ -730,9 +769,123 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                     for (int e = 0; e < 4; ++e) {
                         const int dim = pbase + g + 8 * (e >> 1) + DP * jv;
                         const int qrow = nq * 8 + 2 * l + (e & 1);
-                        if (qrow < p.gq)
-                            p.part_out[(slot * p.gq + qrow) * kHeadDim + dim] = acc[(nq * 8 + mt) * 4 + e] * inv[e & 1];
+                        const float o = acc[(nq * 8 + mt) * 4 + e] * inv[e & 1];
+                        if (qrow < p.gq) {
+                            if (!final_here) {
+                                p.part_out[(slot * p.gq + qrow) * kHeadDim + dim] = o;
+                            } else {
+                                const int64_t oi = ib * p.out_stride_b + (int64_t(ih) * p.gq + qrow) * p.out_stride_h + dim;
+                                if (p.out_dtype == BD_FP16) static_cast<__half *>(p.out)[oi] = __float2half_rn(o);
+                                else if (p.out_dtype == BD_BF16) static_cast<__nv_bfloat16 *>(p.out)[oi] = __float2bfloat16_rn(o);
+                                else static_cast<float *>(p.out)[oi] = o;
+                            }
+                        }
                     }
+                }
+            }
+            if (!final_here) {
+                // publish the partial, count arrivals; the last one merges (same arithmetic as
+                // the reference's combine kernel, flash_fwd_kernel.h:1217-1231, 1280-1298)
+                __threadfence();
+                __syncwarp();
+                int old = 0;
+                if (lane == 0) old = atomicAdd(p.counters + int64_t(ib) * p.h_k + ih, 1);
+                old = __shfl_sync(0xffffffffu, old, 0);
+                if (old == nparts - 1) {
+                    __threadfence();
+                    // Parts sit in consecutive rows, so consecutive slots h_k apart (rows that
+                    // hold no part, possible only with more rows than units, weigh zero).
+                    // Each lane owns 4 head dims; query rows go four at a time, every load of a
+                    // round independent of the others.
+                    const int nrows = pr.c1 - pr.c0 + 1;
+                    const int64_t slot0 = (int64_t(pr.c0) + ib) * p.h_k + ih;
+                    for (int q0 = 0; q0 < p.gq; q0 += 4) {
+                        // pass 1: lane i reads the LSEs of row c0 + i (32 rows per round); one
+                        // round trip to L2 for all of them, then warp reductions
+                        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                        for (int base = 0; base < nrows; base += 32) {
+                            const int i = base + lane;
+                            const bool live = i < nrows && (pr.dense || row_has_part(p.part, ib, pr.c0 + i));
+                            const float *lp = p.part_lse + (slot0 + int64_t(i) * p.h_k) * p.gq + q0;
+#pragma unroll
+                            for (int qq = 0; qq < 4; ++qq) {
+                                float v = (live && q0 + qq < p.gq) ? __ldcg(lp + qq) : -INFINITY;
+#pragma unroll
+                                for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+                                mx[qq] = fmaxf(mx[qq], v);
+                            }
+                        }
+                        // pass 2: weights per lane, then the weighted sum; four rows' worth of
+                        // loads (16 x 16 bytes per lane) are in flight together
+                        float sum[4] = {0.f, 0.f, 0.f, 0.f};
+                        float o[4][4];
+#pragma unroll
+                        for (int qq = 0; qq < 4; ++qq) o[qq][0] = o[qq][1] = o[qq][2] = o[qq][3] = 0.f;
+                        for (int base = 0; base < nrows; base += 32) {
+                            const int i = base + lane;
+                            const bool live = i < nrows && (pr.dense || row_has_part(p.part, ib, pr.c0 + i));
+                            const float *lp = p.part_lse + (slot0 + int64_t(i) * p.h_k) * p.gq + q0;
+                            float w[4];
+#pragma unroll
+                            for (int qq = 0; qq < 4; ++qq)
+                                w[qq] = (live && q0 + qq < p.gq && mx[qq] != -INFINITY) ? __expf(__ldcg(lp + qq) - mx[qq]) : 0.f;
+                            const int cnt = min(32, nrows - base);
+                            for (int j0 = 0; j0 < cnt; j0 += 4) {
+                                float4 v[4][4];
+                                float wj[4][4];
+#pragma unroll
+                                for (int jj = 0; jj < 4; ++jj) {
+                                    const int64_t sl = slot0 + int64_t(base + j0 + jj) * p.h_k;
+#pragma unroll
+                                    for (int qq = 0; qq < 4; ++qq) {
+                                        wj[jj][qq] = __shfl_sync(0xffffffffu, w[qq], (j0 + jj) & 31);
+                                        if (j0 + jj >= cnt) wj[jj][qq] = 0.f;
+                                        v[jj][qq] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                        if (wj[jj][qq] != 0.f)
+                                            v[jj][qq] = __ldcg(reinterpret_cast<const float4 *>(
+                                                p.part_out + (sl * p.gq + q0 + qq) * kHeadDim + 4 * lane));
+                                    }
+                                }
+#pragma unroll
+                                for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+                                    for (int qq = 0; qq < 4; ++qq) {
+                                        sum[qq] += wj[jj][qq];
+                                        o[qq][0] = fmaf(wj[jj][qq], v[jj][qq].x, o[qq][0]);
+                                        o[qq][1] = fmaf(wj[jj][qq], v[jj][qq].y, o[qq][1]);
+                                        o[qq][2] = fmaf(wj[jj][qq], v[jj][qq].z, o[qq][2]);
+                                        o[qq][3] = fmaf(wj[jj][qq], v[jj][qq].w, o[qq][3]);
+                                    }
+                            }
+                        }
+#pragma unroll
+                        for (int qq = 0; qq < 4; ++qq) {
+                            if (q0 + qq >= p.gq) continue;
+                            float lse_f = -INFINITY;
+                            if (mx[qq] != -INFINITY) {
+                                const float inv = 1.0f / sum[qq];
+                                o[qq][0] *= inv; o[qq][1] *= inv; o[qq][2] *= inv; o[qq][3] *= inv;
+                                lse_f = mx[qq] + logf(sum[qq]);
+                            }
+                            const int64_t hq = int64_t(ih) * p.gq + q0 + qq;
+                            const int64_t oi = ib * p.out_stride_b + hq * p.out_stride_h + 4 * lane;
+                            if (p.out_dtype == BD_FP16) {
+                                __half2 a = __floats2half2_rn(o[qq][0], o[qq][1]), b2 = __floats2half2_rn(o[qq][2], o[qq][3]);
+                                *reinterpret_cast<uint2 *>(static_cast<__half *>(p.out) + oi) =
+                                    make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b2));
+                            } else if (p.out_dtype == BD_BF16) {
+                                __nv_bfloat162 a = __floats2bfloat162_rn(o[qq][0], o[qq][1]),
+                                               b2 = __floats2bfloat162_rn(o[qq][2], o[qq][3]);
+                                *reinterpret_cast<uint2 *>(static_cast<__nv_bfloat16 *>(p.out) + oi) =
+                                    make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b2));
+                            } else {
+                                *reinterpret_cast<float4 *>(static_cast<float *>(p.out) + oi) =
+                                    make_float4(o[qq][0], o[qq][1], o[qq][2], o[qq][3]);
+                            }
+                            if (lane == 0 && p.lse) p.lse[int64_t(ib) * p.h + hq] = lse_f;
+                        }
+                    }
+                    if (lane == 0) p.counters[int64_t(ib) * p.h_k + ih] = 0;   // ready for the next step
                 }
             }
         }

@@ -43,6 +43,12 @@ struct PackParams {
 // empty sequences at the very end) and lands in that row's partial.  The combine
 // kernel walks the same arithmetic to find the parts.
 // ---------------------------------------------------------------------------
+// Non-negative 64-bit quotient; takes the cheap 32-bit divide when both fit (they
+// almost always do: unit counts and row counts), the emulated one otherwise.
+BD_HD int64_t div_nn(int64_t a, int64_t b) {
+    return ((a | b) >> 32) == 0 ? int64_t(uint32_t(a) / uint32_t(b)) : a / b;
+}
+
 struct Partition {
     const int32_t *table;     // ragged: (first unit, unit count) per sequence, then (T, 0); null when uniform
     int32_t b;
@@ -53,9 +59,9 @@ struct Partition {
     BD_HD int64_t first(int ib) const { return table ? int64_t(table[2 * ib]) : int64_t(ib) * n_uniform; }
     BD_HD int32_t count(int ib) const { return table ? table[2 * ib + 1] : n_uniform; }
     // first unit of row c (c == R gives T)
-    BD_HD int64_t row_begin(int c, int64_t T) const { return (int64_t(c) * T) / R; }
+    BD_HD int64_t row_begin(int c, int64_t T) const { return div_nn(int64_t(c) * T, R); }
     // row that holds unit f (0 <= f < T)
-    BD_HD int32_t row_of(int64_t f, int64_t T) const { return int32_t(((f + 1) * R - 1) / T); }
+    BD_HD int32_t row_of(int64_t f, int64_t T) const { return int32_t(div_nn((f + 1) * R - 1, T)); }
 };
 
 // One segment of a row: units [u0, u1) of sequence ib (u1 <= u0: no pack blocks,
@@ -83,7 +89,7 @@ struct SegWalk {
     // smallest ib with first(ib) >= f0 or first(ib) + count(ib) > f0
     BD_HD int32_t find_start() const {
         const Partition &pt = *ptp;
-        if (!pt.table) return pt.n_uniform > 0 ? int32_t(f0 / pt.n_uniform) : 0;
+        if (!pt.table) return pt.n_uniform > 0 ? int32_t(div_nn(f0, pt.n_uniform)) : 0;
         int32_t lo = 0, hi = pt.b;
         while (lo < hi) {
             const int32_t mid = (lo + hi) >> 1;
@@ -112,24 +118,40 @@ struct SegWalk {
     }
 };
 
-// Rows that hold a part of sequence ib (the combine side of the same arithmetic):
-// calls f(c) for every row c whose range overlaps the sequence's units.  A
-// sequence without pack blocks but with a tail has one part, in the row that
-// owns its tail.
-template <class F>
-BD_HD void for_each_part(const Partition &pt, int ib, bool has_tail, F &&f) {
+// Rows that hold a part of sequence ib (the merge side of the same arithmetic).
+// A sequence without pack blocks but with a tail has one part, in the row that owns
+// its tail.  When every row has blocks (T >= R, the normal case) the parts are the
+// consecutive rows c0 .. c1; with more rows than units some rows in between are empty.
+struct PartRange {
+    int32_t c0, c1;           // inclusive; c1 < c0: no part
+    bool dense;               // every row of the range holds a part
+};
+BD_HD PartRange part_range(const Partition &pt, int ib, bool has_tail) {
     const int64_t T = pt.total();
     const int64_t first = pt.first(ib), n = pt.count(ib);
+    PartRange r{0, -1, true};
     if (n > 0 && T > 0) {
-        const int c0 = pt.row_of(first, T), c1 = pt.row_of(first + n - 1, T);
-        for (int c = c0; c <= c1; ++c) {
-            const int64_t b0 = pt.row_begin(c, T), b1 = pt.row_begin(c + 1, T);
-            const int64_t lo = b0 > first ? b0 : first, hi = b1 < first + n ? b1 : first + n;
-            if (hi > lo) f(c);                 // rows without blocks exist when there are more rows than units
-        }
+        r.c0 = pt.row_of(first, T);
+        r.c1 = pt.row_of(first + n - 1, T);
+        r.dense = T >= pt.R;
     } else if (has_tail) {
-        f(T > 0 ? pt.row_of(first < T ? first : T - 1, T) : pt.R - 1);
+        r.c0 = r.c1 = (T > 0 ? pt.row_of(first < T ? first : T - 1, T) : pt.R - 1);
     }
+    return r;
+}
+BD_HD bool row_has_part(const Partition &pt, int ib, int c) {
+    const int64_t T = pt.total();
+    const int64_t first = pt.first(ib), n = pt.count(ib);
+    if (n <= 0) return true;                   // the single tail part
+    const int64_t b0 = pt.row_begin(c, T), b1 = pt.row_begin(c + 1, T);
+    const int64_t lo = b0 > first ? b0 : first, hi = b1 < first + n ? b1 : first + n;
+    return hi > lo;
+}
+template <class F>
+BD_HD void for_each_part(const Partition &pt, int ib, bool has_tail, F &&f) {
+    const PartRange r = part_range(pt, ib, has_tail);
+    for (int c = r.c0; c <= r.c1; ++c)
+        if (r.dense || row_has_part(pt, ib, c)) f(c);
 }
 
 struct DecodeParams {
@@ -153,20 +175,12 @@ struct DecodeParams {
     Partition part;
     float *part_out;              // [(R + b) * h_k segment slots][gq][128] fp32, normalised
     float *part_lse;              // [(R + b) * h_k][gq]
-    int32_t *status;
-};
-
-struct CombineParams {
-    const float *part_out, *part_lse;
-    void *out;
-    float *lse;
+    int32_t *counters;            // [b * h_k] parts arrived per (sequence, KV head); zero between steps
+    void *out;                    // (b, h, d) final result
+    float *lse;                   // optional (b, h)
     int64_t out_stride_b, out_stride_h;
-    const int32_t *res_lens;      // per-sequence tail lengths, or null
-    int32_t res_len;              // tail length when res_lens is null (0: no tail)
-    int32_t has_tail;             // a tail buffer was given
-    int32_t b, h, h_k, gq;
     int32_t out_dtype;
-    Partition part;
+    int32_t *status;
 };
 
 struct PrefixParams {
@@ -190,7 +204,6 @@ cudaError_t launch_prefix(const PrefixParams &p, cudaStream_t stream);
 cudaError_t launch_decode(const DecodeParams &p, const CUtensorMap &kmap, const CUtensorMap &vmap,
                           int bits, int group, cudaStream_t stream);
 int decode_ctas_per_sm(int bits, int group, int gq);
-cudaError_t launch_combine(const CombineParams &p, cudaStream_t stream);
 cudaError_t launch_combine_parts(const CombinePartsParams &p, cudaStream_t stream);
 
 }  // namespace bd

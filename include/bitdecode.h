@@ -100,13 +100,15 @@ int bd_pack(const bd_pack_args *args, bd_stream_t stream);
  * Query head hq reads KV head hq / (h / h_k).  The reference has neither the
  * tail, nor per-sequence lengths, nor a returned LSE; they are extensions.
  *
- * The workspace (bd_decode_workspace_bytes) starts with one status word (16
- * bytes reserved) followed by the per-sequence block table (ragged batches) and
- * the partial results of every range.  The caller zeroes
- * the first 16 bytes once after allocating it; bd_decode only ever writes a
- * non-zero error code there (BD_ERR_TIMEOUT), so the hot path has no memset.
- * The same workspace must not be used by two decode calls that can overlap on
- * the device.
+ * The workspace (bd_decode_workspace_bytes) holds one status word, the arrival
+ * counters of the in-kernel merge, the per-sequence block table (ragged
+ * batches) and the partial results of every range.  The caller zeroes it once
+ * after allocating it, and again before using it with a different (b, h_k) or
+ * switching cache_seqlens on or off (the layout moves): every call leaves the
+ * counters at zero again and only
+ * ever writes a non-zero error code (BD_ERR_TIMEOUT) to the status word, so the
+ * hot path has no memset.  After BD_ERR_TIMEOUT zero it again.  The same
+ * workspace must not be used by two decode calls that can overlap on the device.
  */
 typedef struct bd_decode_args {
     const void *q;            /* (b, h, d) fp16 / bf16 */
