@@ -19,6 +19,7 @@ EXPORTS = (
     "bd_pack", "bd_decode", "bd_decode_workspace_bytes", "bd_plan_splits",
     "bd_combine", "bd_read_status", "bd_strerror", "bd_version",
     "bd_partition_segments", "bd_partition_parts",
+    "bd_decode_noalloc", "bd_noalloc_scratch_bytes",
 )
 
 
@@ -92,6 +93,10 @@ def load():
     lib.bd_pack.restype = C.c_int
     lib.bd_decode.argtypes = [C.POINTER(DecodeArgs), C.c_void_p]
     lib.bd_decode.restype = C.c_int
+    lib.bd_decode_noalloc.argtypes = [C.POINTER(DecodeArgs), C.c_void_p]
+    lib.bd_decode_noalloc.restype = C.c_int
+    lib.bd_noalloc_scratch_bytes.argtypes = []
+    lib.bd_noalloc_scratch_bytes.restype = C.c_size_t
     lib.bd_decode_workspace_bytes.argtypes = [C.POINTER(DecodeArgs)]
     lib.bd_decode_workspace_bytes.restype = C.c_size_t
     lib.bd_plan_splits.argtypes = [C.c_int, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int]

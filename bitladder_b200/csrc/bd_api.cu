@@ -251,6 +251,8 @@ const char *bd_strerror(int code) {
         case BD_ERR_CUDA: return "a CUDA runtime or driver call failed";
         case BD_ERR_DEVICE: return "device is not compute capability 10.x";
         case BD_ERR_TIMEOUT: return "a bounded wait inside a kernel ran out";
+        case BD_ERR_SCRATCH_LIMIT: return "this call needs more scratch than the library's fixed area holds "
+                                          "(bd_noalloc_scratch_bytes); use bd_decode with a workspace";
         default: return "unknown error";
     }
 }
@@ -388,6 +390,67 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     if (err != cudaSuccess) return BD_ERR_CUDA;
 
     return BD_OK;
+}
+
+// ---------------------------------------------------------------------------
+// bd_decode_noalloc: decode with the library's own fixed scratch area.
+//
+// Some callers cannot give bd_decode a workspace because they cannot allocate
+// device memory where they call it: a serving runtime that has handed every free
+// byte to its KV-cache pool, code on a latency path that must not touch the
+// allocator, a plugin whose host forbids cudaMalloc after start-up.  For them the
+// scratch lives in a file-scope device array, part of the loaded library image,
+// so every GPU that loads the library holds these bytes until the process ends.
+//
+// The array's name is only a host-side handle, not a device address; the address
+// kernels can use comes from cudaGetSymbolAddress, asked once per device (with
+// that device current) the first time this entry point runs there.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_noalloc_scratch[BD_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+void *noalloc_scratch_address(int *rc_out) {
+    static void *ptr[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { *rc_out = BD_ERR_CUDA; return nullptr; }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ptr[dev]) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) {
+            *rc_out = BD_ERR_CUDA;
+            return nullptr;
+        }
+        ptr[dev] = p;
+    }
+    *rc_out = BD_OK;
+    return ptr[dev];
+}
+}  // namespace
+
+size_t bd_noalloc_scratch_bytes(void) { return BD_NOALLOC_SCRATCH_BYTES; }
+
+int bd_decode_noalloc(const bd_decode_args *a, bd_stream_t stream_) {
+    int rc = check_decode_args(a);
+    if (rc != BD_OK) return rc;
+    DeviceInfo info;
+    rc = current_device_info(info);
+    if (rc != BD_OK) return rc;
+    if (info.cc_major != 10) return BD_ERR_DEVICE;
+    DecodePlan plan;
+    make_plan(a, info.sm_count, plan);
+    if (plan.total_bytes > BD_NOALLOC_SCRATCH_BYTES) return BD_ERR_SCRATCH_LIMIT;
+    void *scratch = noalloc_scratch_address(&rc);
+    if (rc != BD_OK) return rc;
+    // The area keeps whatever the previous call left (partials of another shape may sit
+    // where this call's counters go): clear the status word and the arrival counters,
+    // the only bytes that must start at zero.  No allocation: a memset node on the stream.
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (cudaMemsetAsync(scratch, 0, plan.off_table, stream) != cudaSuccess) return BD_ERR_CUDA;
+    bd_decode_args args = *a;
+    args.workspace = scratch;
+    args.workspace_bytes = BD_NOALLOC_SCRATCH_BYTES;
+    return bd_decode(&args, stream_);
 }
 
 int bd_combine(const bd_combine_args *a, bd_stream_t stream) {

@@ -47,6 +47,7 @@ extern "C" {
 #define BD_ERR_CUDA         -5   /* a CUDA runtime / driver call failed */
 #define BD_ERR_DEVICE       -6   /* not an sm_100 device */
 #define BD_ERR_TIMEOUT      -7   /* a bounded device-side wait ran out (see bd_read_status) */
+#define BD_ERR_SCRATCH_LIMIT -8  /* bd_decode_noalloc: the call needs more than the fixed scratch area */
 
 /* element types */
 #define BD_FP16 0
@@ -141,6 +142,37 @@ int bd_decode(const bd_decode_args *args, bd_stream_t stream);
 
 /* Bytes of workspace bd_decode needs for these arguments (0 on invalid input). */
 size_t bd_decode_workspace_bytes(const bd_decode_args *args);
+
+/*
+ * bd_decode for callers that cannot allocate device memory.  (No counterpart in
+ * the reference, whose decode call allocates its split buffers itself on every
+ * call.)
+ *
+ * bd_decode needs a caller-allocated workspace.  Some callers have nowhere to
+ * get one at the point of the call: a serving runtime that has already given
+ * every free byte of HBM to its KV-cache pool, a latency path that must never
+ * enter the allocator, a plugin host that forbids cudaMalloc after start-up.
+ * bd_decode_noalloc takes the same arguments (args->workspace and
+ * args->workspace_bytes are ignored) and keeps the partial results, arrival
+ * counters and sequence table in a fixed area of BD_NOALLOC_SCRATCH_BYTES that is
+ * part of the library image: every GPU that loads the library carries those
+ * bytes until the process exits, whether this entry point is used or not.
+ *
+ *  - It calls no cudaMalloc / cudaFree and no allocating library routine; per
+ *    call it queues one small memset (status word and counters) and the decode
+ *    kernel(s) on `stream`.
+ *  - The first call on each device looks up the area's device address (with
+ *    that device current).  Make that first call outside any stream capture.
+ *  - A call whose shapes need more than BD_NOALLOC_SCRATCH_BYTES (large batch *
+ *    head counts; bd_decode_workspace_bytes tells) fails with
+ *    BD_ERR_SCRATCH_LIMIT and launches nothing; use bd_decode for those.
+ *  - There is one area per device, shared by every call and every stream, and it
+ *    keeps what the last call left.  Two calls that can overlap on the same
+ *    device race on it: serialise them (same stream, or events).
+ */
+#define BD_NOALLOC_SCRATCH_BYTES (8u << 20)
+int bd_decode_noalloc(const bd_decode_args *args, bd_stream_t stream);
+size_t bd_noalloc_scratch_bytes(void);
 
 /*
  * How bd_decode splits the sequence dimension when num_splits == 0; takes the
