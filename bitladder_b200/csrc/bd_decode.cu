@@ -329,7 +329,23 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             res_n = p.res_lens ? p.res_lens[ib] : p.res_len;
             res_n = min(max(res_n, 0), kTailMax);
         }
-        if (sg.u1 <= sg.u0 && res_n == 0) continue;   // nothing of this sequence to do here
+        if (sg.u1 <= sg.u0 && res_n == 0) {
+            // Nothing of this sequence to stream here.  If it has no tokens at all, the row
+            // that owns its (empty) tail writes the defined result: out = 0, lse = -inf.
+            if (sg.owns_tail && p.part.count(ib) == 0 && warp == 0) {
+                for (int qrow = 0; qrow < p.gq; ++qrow) {
+                    const int64_t hq = int64_t(ih) * p.gq + qrow;
+                    const int64_t oi = ib * p.out_stride_b + hq * p.out_stride_h + 4 * lane;
+                    if (p.out_dtype == BD_FP32) {
+                        *reinterpret_cast<float4 *>(static_cast<float *>(p.out) + oi) = make_float4(0.f, 0.f, 0.f, 0.f);
+                    } else {                       // fp16 and bf16 zeros are the same bits
+                        *reinterpret_cast<uint2 *>(static_cast<uint16_t *>(p.out) + oi) = make_uint2(0u, 0u);
+                    }
+                    if (lane == 0 && p.lse) p.lse[int64_t(ib) * p.h + hq] = -INFINITY;
+                }
+            }
+            continue;
+        }
         int seqlen = p.s;
         if (p.cache_seqlens) seqlen = min(max(p.cache_seqlens[ib], 0), p.s);
 

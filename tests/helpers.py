@@ -64,3 +64,40 @@ def u16(t: torch.Tensor) -> np.ndarray:
 def f32_as_u16(t: torch.Tensor) -> np.ndarray:
     """float32-typed parameter storage -> numpy uint16 view (fp16 bit patterns)."""
     return t.detach().cpu().contiguous().numpy().view(np.uint16)
+
+
+# ---------------------------------------------------------------------------
+# golden fixtures (tests/golden/pack_decode_small.npz, made by tests/golden/make_golden.py)
+# ---------------------------------------------------------------------------
+import os as _os
+
+GOLDEN_PATH = _os.path.join(_os.path.dirname(_os.path.abspath(__file__)), "golden", "pack_decode_small.npz")
+
+
+def load_golden():
+    """{case name: {array name: ndarray}} with meta decoded into a dict."""
+    blob = np.load(GOLDEN_PATH)
+    cases = {}
+    for key in blob.files:
+        name, arr = key.split("/", 1)
+        cases.setdefault(name, {})[arr] = blob[key]
+    for c in cases.values():
+        m = c.pop("meta")
+        c["cfg"] = dict(bits=int(m[0]), group=int(m[1]), dtype="bf16" if m[2] else "fp16", b=int(m[3]), s=int(m[4]),
+                        h=int(m[5]), h_k=int(m[6]), res=int(m[7]), ragged=bool(m[8]))
+    return cases
+
+
+def golden_input(case, name):
+    """Input array of a golden case the way the oracles take it (fp16 array, or bf16 bit patterns)."""
+    if name not in case:
+        return None
+    a = case[name]
+    return a.view(np.float16) if case["cfg"]["dtype"] == "fp16" else a
+
+
+def golden_torch(case, name, device="cpu"):
+    if name not in case:
+        return None
+    tdt = torch.float16 if case["cfg"]["dtype"] == "fp16" else torch.bfloat16
+    return torch.from_numpy(case[name].view(np.int16).copy()).view(tdt).to(device)

@@ -1,0 +1,109 @@
+"""GPU: the headline configuration at FULL size (batch 8, 32/8 heads, 32768 packed tokens + 64-token
+tail), where the numpy oracle is too slow for every element: one sequence is checked element by
+element against the C oracle, the rest through properties that do not depend on size."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle
+from tests import gpu_util as G, helpers as H
+
+pytestmark = pytest.mark.gpu
+
+B_, S_, H_, HK_, RES_ = 8, 32768, 32, 8, 64
+
+
+@pytest.fixture(scope="module")
+def c2():
+    import bitladder_b200 as B
+    g = torch.Generator(device="cuda").manual_seed(1002)
+    bufs = B.alloc_packed_cache(B_, S_, HK_, 128, 4, 128, device="cuda")
+    keep = {}
+    for ib in range(B_):
+        k = torch.randn(1, S_, HK_, 128, generator=g, device="cuda").half()
+        v = torch.randn(1, S_, HK_, 128, generator=g, device="cuda").half()
+        B.kvcache_pack_int(k, bufs[0][ib:ib + 1], bufs[1][ib:ib + 1], v, bufs[2][ib:ib + 1], bufs[3][ib:ib + 1],
+                           None, None, S_, "k-channel", 128, 4)
+        if ib == 3:
+            keep = dict(k=k.cpu(), v=v.cpu())
+    q = torch.randn(B_, 1, H_, 128, generator=g, device="cuda").half()
+    k_res = torch.randn(B_, RES_, HK_, 128, generator=g, device="cuda").half()
+    v_res = torch.randn(B_, RES_, HK_, 128, generator=g, device="cuda").half()
+    torch.cuda.synchronize()
+    return dict(B=B, bufs=bufs, q=q, k_res=k_res, v_res=v_res, keep=keep)
+
+
+def _decode(c, **kw):
+    return c["B"].fwd_kvcache_int(c["q"], *c["bufs"], None, 1 / math.sqrt(128), "k-channel", 128, 4,
+                                  k_res=c["k_res"], v_res=c["v_res"], return_lse=True, **kw)
+
+
+def test_one_full_length_sequence_against_the_oracle(c2):
+    out, lse = _decode(c2)
+    ib = 3
+    kp = c_oracle.quantize_pack(c2["keep"]["k"].numpy(), c2["keep"]["v"].numpy(), 4, 128)
+    assert np.array_equal(H.u16(c2["bufs"][0][ib:ib + 1]), kp["k_pack"])           # pack at full length
+    assert np.array_equal(H.u16(c2["bufs"][2][ib:ib + 1]), kp["v_pack"])
+    o_ref, l_ref = c_oracle.decode(c2["q"][ib:ib + 1].cpu().numpy(), kp["k_pack"], kp["k_params"], kp["v_pack"],
+                                   kp["v_params"], 1 / math.sqrt(128), 4, 128,
+                                   k_res=c2["k_res"][ib:ib + 1].cpu().numpy(), v_res=c2["v_res"][ib:ib + 1].cpu().numpy())
+    eo, el = G.errs(out[ib:ib + 1], lse[ib:ib + 1], o_ref, l_ref)
+    print(f"full-size sequence: max|dO|={eo:.3e} max|dLSE|={el:.3e}")
+    assert eo <= 2e-3 and el <= 2e-3
+
+
+def test_result_does_not_depend_on_how_the_sequence_is_cut(c2):
+    base, base_lse = _decode(c2)
+    for splits in (1, 3, 16):
+        out, lse = _decode(c2, num_splits=splits)
+        assert (out.float() - base.float()).abs().max().item() <= 5e-4
+        assert (lse - base_lse).abs().max().item() <= 5e-4
+
+
+def test_sequences_are_independent_and_runs_are_deterministic(c2):
+    a, la = _decode(c2)
+    b, lb = _decode(c2)
+    assert torch.equal(a, b) and torch.equal(la, lb)
+    cs = torch.full((B_,), S_, dtype=torch.int32, device="cuda")
+    cs[5] = 12345                                  # shortening one sequence must not move the others
+    c, lc = _decode(c2, cache_seqlens=cs)
+    others = [i for i in range(B_) if i != 5]
+    assert (c[others].float() - a[others].float()).abs().max().item() <= 5e-4
+    assert (lc[5] < la[5]).all()                   # fewer keys: smaller log-sum-exp
+
+
+def test_lse_of_the_whole_is_logsumexp_of_the_parts(c2):
+    """Attention over tokens [0, n) and the tail, merged with attention over nothing else, must obey
+    LSE(all) = log(exp(LSE(first n)) + exp(LSE(rest))): checked by cutting at a block boundary."""
+    B = c2["B"]
+    full, full_lse = _decode(c2)
+    n = 128 * 100
+    cs = torch.full((B_,), n, dtype=torch.int32, device="cuda")
+    p1 = B.fwd_kvcache_int(c2["q"], *c2["bufs"], None, 1 / math.sqrt(128), "k-channel", 128, 4,
+                           cache_seqlens=cs, out_dtype=torch.float32, return_lse=True)
+    kp, kprm, vp, vprm = c2["bufs"]
+    rest = [kp[:, n // 4:].contiguous(), kprm[:, n // 128:].contiguous(), vp[:, n:].contiguous(),
+            vprm[:, :, :, n:].contiguous()]
+    p2 = B.fwd_kvcache_int(c2["q"], *rest, None, 1 / math.sqrt(128), "k-channel", 128, 4, k_res=c2["k_res"],
+                           v_res=c2["v_res"], out_dtype=torch.float32, return_lse=True)
+    out, lse = B.combine_partials([p1[0], p2[0]], [p1[1], p2[1]], torch.float16, return_lse=True)
+    assert (lse - torch.logaddexp(p1[1], p2[1])).abs().max().item() <= 1e-5
+    assert (lse - full_lse).abs().max().item() <= 1e-3
+    assert (out.float() - full.float()).abs().max().item() <= 1e-3
+
+
+def test_constant_values_come_back_exactly(c2):
+    """Softmax weights sum to one: with every V row (packed and tail) equal to the same constant the
+    output is that constant whatever K is -- a check of the normalisation over 32768 + 64 tokens that
+    needs no oracle (a constant group quantizes to scale 0, zero = the constant, so it is exact)."""
+    B = c2["B"]
+    v = torch.full((1, S_, HK_, 128), 0.75, dtype=torch.float16, device="cuda")
+    vbufs = B.alloc_packed_cache(1, S_, HK_, 128, 4, 128, device="cuda")
+    B.kvcache_pack_int(v, vbufs[0], vbufs[1], v, vbufs[2], vbufs[3], None, None, S_, "k-channel", 128, 4)
+    bufs = (c2["bufs"][0][:1], c2["bufs"][1][:1], vbufs[2], vbufs[3])
+    vres = torch.full((1, RES_, HK_, 128), 0.75, dtype=torch.float16, device="cuda")
+    out = B.fwd_kvcache_int(c2["q"][:1], *bufs, None, 1 / math.sqrt(128), "k-channel", 128, 4,
+                            k_res=c2["k_res"][:1], v_res=vres)
+    assert (out.float() - 0.75).abs().max().item() <= 1e-3
