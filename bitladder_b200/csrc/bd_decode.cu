@@ -46,8 +46,15 @@
 
 namespace bd {
 
-constexpr int kWarps = 4;
-constexpr int kDecodeThreads = kWarps * 32;
+#ifndef BD_MAX_WARPS
+#define BD_MAX_WARPS 12
+#endif
+// Streaming warps per CTA: as many as fit one CTA per SM, at most this (three per
+// scheduler; 384 threads keep 168 registers each).  All warps of an SM then belong to
+// one CTA and have the same age: with several CTAs per SM the scheduler favoured the
+// warps of the CTA that was launched first and the others finished up to 40 % later.
+constexpr int kMaxWarps = BD_MAX_WARPS;
+constexpr int kSmemLimit = 232448;     // 227 KB of shared memory per CTA
 constexpr int kTailMax = 256;          // longest unquantized tail the kernel accepts
 constexpr float kRescaleSlack = 8.0f;  // keep a stale row max until it is exceeded by 2^8
 
@@ -66,11 +73,19 @@ struct Cfg {
     static constexpr int QROWS = NQT * 8;
     static constexpr int NACC = 8 * NQT * 4 + 4 * NQT;  // floats per thread handed over in a merge
     // per warp: one K tile and one V tile, then their scales/zeros
-    static constexpr size_t OFF_PRM = size_t(kWarps) * 2 * CODE_BYTES;
-    static constexpr size_t OFF_XCHG = OFF_PRM + size_t(kWarps) * 2 * PRM_BYTES;
+    static constexpr int WARP_BYTES = 2 * CODE_BYTES + 2 * PRM_BYTES + 16;
+    static constexpr int FIT = (kSmemLimit - NACC * 32 * 4 - 16) / WARP_BYTES;
+    // two query tiles need more than 168 registers per thread: eight warps leave 255
+    static constexpr int CAP = NQT == 1 ? kMaxWarps : (kMaxWarps < 8 ? kMaxWarps : 8);
+    static constexpr int WARPS = FIT < CAP ? FIT : CAP;
+    static constexpr int THREADS = WARPS * 32;
+    static constexpr size_t OFF_PRM = size_t(WARPS) * 2 * CODE_BYTES;
+    static constexpr size_t OFF_XCHG = OFF_PRM + size_t(WARPS) * 2 * PRM_BYTES;
     static constexpr size_t OFF_BAR = OFF_XCHG + size_t(NACC) * 32 * 4;
-    static constexpr size_t SMEM = OFF_BAR + 2 * kWarps * 8 + 16;
-    static constexpr int CTAS_PER_SM = (SMEM + 1024) * 3 <= 233472 ? 3 : 2;
+    static constexpr size_t SMEM = OFF_BAR + 2 * WARPS * 8 + 16;
+    static constexpr int CTAS_PER_SM = (SMEM + 1024) * 3 <= 233472 ? 3 : ((SMEM + 1024) * 2 <= 233472 ? 2 : 1);
+    static_assert(WARPS >= 2 && WARPS <= 14, "named barriers 1..WARPS");
+    static_assert(SMEM <= size_t(kSmemLimit), "shared memory");
 };
 
 // Field j of a packed word as two fp16 lanes.  `wsh` is the word shifted right
@@ -175,61 +190,49 @@ __device__ __forceinline__ bool softmax_step(float (&t)[NT][4], float (&m_run)[2
     return any;
 }
 
-__device__ __forceinline__ uint4 ldg128_or_zero(const uint16_t *p, bool ok, bool bf16) {
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (ok) {
-        v = __ldg(reinterpret_cast<const uint4 *>(p));
-        if (bf16) {
-            v.x = bf16x2_to_f16x2(v.x); v.y = bf16x2_to_f16x2(v.y);
-            v.z = bf16x2_to_f16x2(v.z); v.w = bf16x2_to_f16x2(v.w);
-        }
-    }
-    return v;
-}
-__device__ __forceinline__ uint32_t ldg32_or_zero(const uint16_t *p, bool ok, bool bf16) {
-    uint32_t v = 0;
-    if (ok) {
-        v = __ldg(reinterpret_cast<const unsigned int *>(p));
-        if (bf16) v = bf16x2_to_f16x2(v);
-    }
-    return v;
-}
-
-// This warp's position in its stream of pack blocks: walks the row's segments and,
-// inside a segment, every kWarps-th block starting at the warp index.
+// This warp's position in its stream of pack blocks.  The blocks of a row are dealt to
+// the warps round-robin, and the deal continues across the row's segments (`rot` is the
+// warp that gets the first block of the current segment), so that the warps' block
+// counts differ by at most one over the whole row.
+template <int WARPS>
 struct BlockCursor {
     SegWalk walk;
     Segment sg;
     int32_t u;
+    int32_t rot;
     bool valid;
 
+    __device__ __forceinline__ bool seek(int warp) {
+        while (walk.next(sg)) {
+            int off = warp - rot;
+            if (off < 0) off += WARPS;
+            u = sg.u0 + off;
+            if (sg.u1 > sg.u0) rot = (rot + (sg.u1 - sg.u0)) % WARPS;
+            if (u < sg.u1) return true;
+        }
+        return false;
+    }
     __device__ __forceinline__ void init(const Partition &pt, int row, int warp) {
         walk.init(pt, row);
-        valid = false;
-        while (walk.next(sg)) {
-            u = sg.u0 + warp;
-            if (u < sg.u1) { valid = true; return; }
-        }
+        rot = 0;
+        valid = seek(warp);
     }
     __device__ __forceinline__ void advance(int warp) {
-        u += kWarps;
+        u += WARPS;
         if (u < sg.u1) return;
-        valid = false;
-        while (walk.next(sg)) {
-            u = sg.u0 + warp;
-            if (u < sg.u1) { valid = true; return; }
-        }
+        valid = seek(warp);
     }
 };
 
 template <int BITS, int GROUP, int NQT>
-__global__ void __launch_bounds__(kDecodeThreads, Cfg<BITS, GROUP, NQT>::CTAS_PER_SM)
+__global__ void __launch_bounds__(Cfg<BITS, GROUP, NQT>::THREADS, Cfg<BITS, GROUP, NQT>::CTAS_PER_SM)
 bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                  const __grid_constant__ CUtensorMap vmap) {
     using C = Cfg<BITS, GROUP, NQT>;
     constexpr int P = C::P, NB = C::NB, NGK = C::NGK, FPG = C::FPG, NGD = C::NGD, FPGV = C::FPGV;
     constexpr int DP = C::DP, RUNS = C::RUNS, PRM = C::PRM_BYTES, NACC = C::NACC;
     constexpr int SHIFT = (BITS == 4) ? 8 : 10;
+    constexpr int kWarps = C::WARPS;
 
     // The swizzled TMA tiles need a 1024-byte aligned base; dynamic shared memory
     // starts at the beginning of the CTA's window, which is, and the kernel checks it.
@@ -239,7 +242,11 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     float *xchg = reinterpret_cast<float *>(smem + C::OFF_XCHG);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef BD_EXP_ROTHEAD
+    const int ih = blockIdx.x % p.h_k, row = (blockIdx.x / p.h_k + ih * BD_EXP_ROTHEAD) % p.part.R;
+#else
     const int ih = blockIdx.x % p.h_k, row = blockIdx.x / p.h_k;
+#endif
     const int g = lane >> 2, l = lane & 3;
     if ((smem_base & 1023u) != 0) {                      // never seen; refuse rather than read garbage
         if (tid == 0) atomicExch(p.status, BD_ERR_ALIGNMENT);
@@ -264,7 +271,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     }
     __syncthreads();
     // hand-over buffer starts free: warp 0 holds the credit that warp 3 consumes
-    if (warp == 0) bar_arrive(4, 64);
+    if (warp == 0) bar_arrive(kWarps, 64);
 
     // ---- TMA issue (one lane) ------------------------------------------------
     auto issue_k = [&](int ib, int blk) {
@@ -288,7 +295,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     };
 
     // ---- prologue: first block of this warp ------------------------------------
-    BlockCursor ld;
+    BlockCursor<kWarps> ld;
     ld.init(p.part, row, warp);
     if (ld.valid && lane == 0) {
         issue_k(ld.sg.ib, ld.u);
@@ -322,8 +329,12 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     SegWalk walk;
     walk.init(p.part, row);
     Segment sg;
+    int rot = 0;           // warp that takes the first block of the segment (see BlockCursor)
     while (walk.next(sg)) {
         const int ib = sg.ib;
+        int first_off = warp - rot;
+        if (first_off < 0) first_off += kWarps;
+        if (sg.u1 > sg.u0) rot = (rot + (sg.u1 - sg.u0)) % kWarps;
         int res_n = 0;                                // tail tokens this row owns for this sequence
         if (sg.owns_tail && p.k_res != nullptr) {
             res_n = p.res_lens ? p.res_lens[ib] : p.res_len;
@@ -394,23 +405,48 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
         for (int tok0 = 16 * warp; tok0 < res_n; tok0 += 16 * kWarps) {
             const int tA = tok0 + g, tB = tA + 8;
             const bool okA = tA < res_n, okB = tB < res_n;
+            // rows past the end are read from the last valid row (in bounds) and zeroed afterwards,
+            // so that every load below is unconditional and all of them are in flight together
+            const int rA = min(tA, res_n - 1), rB = min(tB, res_n - 1);
             const uint16_t *kres = static_cast<const uint16_t *>(p.k_res) + ib * p.res_stride_b + ih * p.res_stride_h;
             const uint16_t *vres = static_cast<const uint16_t *>(p.v_res) + ib * p.res_stride_b + ih * p.res_stride_h;
+            const uint16_t *kA = kres + int64_t(rA) * p.res_stride_s + 8 * l, *kB = kres + int64_t(rB) * p.res_stride_s + 8 * l;
+            const uint16_t *vA = vres + int64_t(rA) * p.res_stride_s + 2 * l, *vB = vres + int64_t(rB) * p.res_stride_s + 2 * l;
+            uint4 ka[4], kb[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                ka[a] = __ldg(reinterpret_cast<const uint4 *>(kA + 32 * a));
+                kb[a] = __ldg(reinterpret_cast<const uint4 *>(kB + 32 * a));
+            }
+            uint32_t va[16], vb[16];     // word i: dims 8 i + 2 l, + 1 of the two token rows
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                va[i] = __ldg(reinterpret_cast<const unsigned int *>(vA + 8 * i));
+                vb[i] = __ldg(reinterpret_cast<const unsigned int *>(vB + 8 * i));
+            }
+            if (bf16) {
+#pragma unroll
+                for (int a = 0; a < 4; ++a) {
+                    ka[a].x = bf16x2_to_f16x2(ka[a].x); ka[a].y = bf16x2_to_f16x2(ka[a].y);
+                    ka[a].z = bf16x2_to_f16x2(ka[a].z); ka[a].w = bf16x2_to_f16x2(ka[a].w);
+                    kb[a].x = bf16x2_to_f16x2(kb[a].x); kb[a].y = bf16x2_to_f16x2(kb[a].y);
+                    kb[a].z = bf16x2_to_f16x2(kb[a].z); kb[a].w = bf16x2_to_f16x2(kb[a].w);
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) { va[i] = bf16x2_to_f16x2(va[i]); vb[i] = bf16x2_to_f16x2(vb[i]); }
+            }
             float S1[NQT][1][4];
 #pragma unroll
             for (int nq = 0; nq < NQT; ++nq)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) S1[nq][0][e] = 0.f;
 #pragma unroll
-            for (int a = 0; a < 4; ++a) {
-                const uint4 ka = ldg128_or_zero(kres + int64_t(tA) * p.res_stride_s + 32 * a + 8 * l, okA, bf16);
-                const uint4 kb = ldg128_or_zero(kres + int64_t(tB) * p.res_stride_s + 32 * a + 8 * l, okB, bf16);
+            for (int a = 0; a < 4; ++a)
 #pragma unroll
                 for (int nq = 0; nq < NQT; ++nq) {
-                    mma_f16(S1[nq][0], ka.x, kb.x, ka.y, kb.y, qr[nq][a][0], qr[nq][a][1]);
-                    mma_f16(S1[nq][0], ka.z, kb.z, ka.w, kb.w, qr[nq][a][2], qr[nq][a][3]);
+                    mma_f16(S1[nq][0], ka[a].x, kb[a].x, ka[a].y, kb[a].y, qr[nq][a][0], qr[nq][a][1]);
+                    mma_f16(S1[nq][0], ka[a].z, kb[a].z, ka[a].w, kb[a].w, qr[nq][a][2], qr[nq][a][3]);
                 }
-            }
             uint32_t pb[NQT][2];
 #pragma unroll
             for (int nq = 0; nq < NQT; ++nq) {
@@ -428,11 +464,12 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
             for (int mt = 0; mt < 8; ++mt) {
                 const int jv = (BITS == 4) ? (mt & 3) : mt;
-                const int d0 = ((BITS == 4) ? 16 * (mt >> 2) : 0) + DP * jv + 2 * l;   // dims of rows 0-7 (+8: rows 8-15)
-                const uint32_t a0 = movmatrix_trans(ldg32_or_zero(vres + int64_t(tA) * p.res_stride_s + d0, okA, bf16));
-                const uint32_t a1 = movmatrix_trans(ldg32_or_zero(vres + int64_t(tA) * p.res_stride_s + d0 + 8, okA, bf16));
-                const uint32_t a2 = movmatrix_trans(ldg32_or_zero(vres + int64_t(tB) * p.res_stride_s + d0, okB, bf16));
-                const uint32_t a3 = movmatrix_trans(ldg32_or_zero(vres + int64_t(tB) * p.res_stride_s + d0 + 8, okB, bf16));
+                // rows 0-7 of this m-tile are dims d0 .. d0+7, rows 8-15 are d0+8 .. d0+15
+                const int i0 = (((BITS == 4) ? 16 * (mt >> 2) : 0) + DP * jv) / 8;
+                const uint32_t a0 = movmatrix_trans(okA ? va[i0] : 0u);
+                const uint32_t a1 = movmatrix_trans(okA ? va[i0 + 1] : 0u);
+                const uint32_t a2 = movmatrix_trans(okB ? vb[i0] : 0u);
+                const uint32_t a3 = movmatrix_trans(okB ? vb[i0 + 1] : 0u);
                 const float fw = field_weight<BITS>(jv);   // O is kept in the units of its packed field
 #pragma unroll
                 for (int nq = 0; nq < NQT; ++nq) {
@@ -444,7 +481,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             }
         }
 
-        for (int blk = sg.u0 + warp; blk < sg.u1 && !aborted; blk += kWarps) {
+        for (int blk = sg.u0 + first_off; blk < sg.u1 && !aborted; blk += kWarps) {
             const bool need_mask = (blk + 1) * NB > seqlen;
 
             // ------------------------------------------------------------ K phase
@@ -730,27 +767,24 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
             for (int i = 0; i < NACC; ++i) xchg[i * 32 + lane] = acc[i];
         };
-        if (warp == 3) {
-            bar_sync(4, 64);            // buffer free (warp 0 is done with the previous segment)
+        // chain: warp kWarps-1 -> ... -> 1 -> 0.  Named barrier w (1 <= w < kWarps) hands the
+        // buffer from warp w to warp w-1; barrier kWarps is the credit "buffer free" that warp 0
+        // returns to the head of the chain.
+        if (warp == kWarps - 1) {
+            bar_sync(kWarps, 64);       // buffer free (warp 0 is done with the previous segment)
             hand_over();
             __threadfence_block();
-            bar_arrive(1, 64);
-        } else if (warp == 2) {
+            bar_arrive(kWarps - 1, 64);
+        } else if (warp > 0) {
+            bar_sync(warp + 1, 64);
+            merge_in();
+            hand_over();
+            __threadfence_block();
+            bar_arrive(warp, 64);
+        } else {
             bar_sync(1, 64);
             merge_in();
-            hand_over();
-            __threadfence_block();
-            bar_arrive(2, 64);
-        } else if (warp == 1) {
-            bar_sync(2, 64);
-            merge_in();
-            hand_over();
-            __threadfence_block();
-            bar_arrive(3, 64);
-        } else {
-            bar_sync(3, 64);
-            merge_in();
-            bar_arrive(4, 64);
+            bar_arrive(kWarps, 64);
             // How many rows hold a part of this sequence?  One: this is the final result.
             // More: leave a normalised partial; the row that arrives last merges them all.
             bool seq_tail = false;
@@ -974,7 +1008,7 @@ static cudaError_t launch_t(const DecodeParams &p, const CUtensorMap &kmap, cons
         configured[dev] = true;
     }
     const unsigned grid = unsigned(p.part.R) * unsigned(p.h_k);
-    kern<<<grid, kDecodeThreads, C::SMEM, stream>>>(p, kmap, vmap);
+    kern<<<grid, C::THREADS, C::SMEM, stream>>>(p, kmap, vmap);
     return cudaGetLastError();
 }
 
