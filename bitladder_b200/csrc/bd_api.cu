@@ -103,7 +103,7 @@ int plan_rows(int b, int h_k, int64_t max_s, int bits, int sm_count, int ctas_pe
     if (b <= 0 || h_k <= 0 || max_s <= 0) return 1;
     const int nb = pack_block_tokens(bits);
     const int64_t nblk = (max_s + nb - 1) / nb;
-    if (ctas_per_sm <= 0) ctas_per_sm = 3;
+    if (ctas_per_sm <= 0) ctas_per_sm = bd::decode_ctas_per_sm(bits, 128, 4);
     const int64_t slots = int64_t(sm_count) * ctas_per_sm;
     int64_t rows = std::max<int64_t>(1, slots / h_k);
     rows = std::min<int64_t>(rows, std::max<int64_t>(1, (int64_t(b) * nblk + 3) / 4));

@@ -88,25 +88,41 @@ struct Cfg {
     static_assert(SMEM <= size_t(kSmemLimit), "shared memory");
 };
 
-// Field j of a packed word as two fp16 lanes.  `wsh` is the word shifted right
-// by 8 (4-bit) or 10 (2-bit) so that every field lands inside the fp16 mantissa.
+// A packed 32-bit register (two 16-bit words) and the helper word the field extraction
+// needs: 4-bit: the high bytes of both words moved to the low bytes (one byte permute);
+// 2-bit: the register shifted right by 10.
+template <int BITS>
+__device__ __forceinline__ uint32_t aux_word(uint32_t w) {
+    if constexpr (BITS == 4) return __byte_perm(w, 0u, 0x4341u);
+    else return w >> 10;
+}
+// Field j of a packed word as two fp16 lanes, every field inside the fp16 mantissa.
+//
+// 4-bit words are taken apart in PAIRS: an even field comes out together with the odd
+// field above it (f_j + 16 f_{j+1}, a whole byte: still an exact fp16 subnormal), the odd
+// field alone (16 f_{j+1}).  The products are linear, so the even field's sum is the
+// difference of the two accumulators, taken once after the last MMA; that saves the
+// shift and one of the masks on the high byte.  kFieldPairs tells the callers.
 template <int BITS, int J>
-__device__ __forceinline__ uint32_t field(uint32_t w, uint32_t wsh) {
+__device__ __forceinline__ uint32_t field(uint32_t w, uint32_t aux) {
     uint32_t x;
     if constexpr (BITS == 4) {
-        constexpr uint32_t m = (J & 1) ? 0x00f000f0u : 0x000f000fu;
-        x = ((J & 2) ? wsh : w) & m;
+        if constexpr (J == 0) x = w & 0x00ff00ffu;
+        else if constexpr (J == 1) x = w & 0x00f000f0u;
+        else if constexpr (J == 2) x = aux;
+        else x = aux & 0x00f000f0u;
     } else {
         constexpr uint32_t m = 0x00030003u << (2 * (J < 5 ? J : J - 5));
-        x = ((J < 5) ? w : wsh) & m;
+        x = ((J < 5) ? w : aux) & m;
     }
 #if !BD_SUBNORMAL_CODES
-    x |= 0x64006400u;   // 1024 + code * 16^k, then remove the 1024 exactly
+    x |= 0x64006400u;   // 1024 + value, then remove the 1024 exactly
     __half2 h = __hsub2(*reinterpret_cast<__half2 *>(&x), __half2half2(__ushort_as_half(0x6400)));
     x = *reinterpret_cast<uint32_t *>(&h);
 #endif
     return x;
 }
+template <int BITS> constexpr bool kFieldPairs = (BITS == 4);
 // Value of the fp16 lane produced by field<J> divided by the code.
 template <int BITS>
 __host__ __device__ constexpr float field_weight(int j) {
@@ -231,7 +247,6 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     using C = Cfg<BITS, GROUP, NQT>;
     constexpr int P = C::P, NB = C::NB, NGK = C::NGK, FPG = C::FPG, NGD = C::NGD, FPGV = C::FPGV;
     constexpr int DP = C::DP, RUNS = C::RUNS, PRM = C::PRM_BYTES, NACC = C::NACC;
-    constexpr int SHIFT = (BITS == 4) ? 8 : 10;
     constexpr int kWarps = C::WARPS;
 
     // The swizzled TMA tiles need a 1024-byte aligned base; dynamic shared memory
@@ -476,7 +491,12 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                     float ot[4] = {0.f, 0.f, 0.f, 0.f};
                     mma_f16(ot, a0, a1, a2, a3, pb[nq][0], pb[nq][1]);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) O[nq][mt][e] = fmaf(ot[e], fw, O[nq][mt][e]);
+                    for (int e = 0; e < 4; ++e) {
+                        O[nq][mt][e] = fmaf(ot[e], fw, O[nq][mt][e]);
+                        if constexpr (kFieldPairs<BITS>) {          // the accumulator below holds the pair sum
+                            if (mt & 1) O[nq][mt - 1][e] = fmaf(ot[e], fw, O[nq][mt - 1][e]);
+                        }
+                    }
                 }
             }
         }
@@ -518,16 +538,21 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                     }
             }
 
+            // Units (16 pack rows) that share one softmax step: both of a 4-bit block (one
+            // step per block), one of a 2-bit block (its 8 fields fill the registers).
+            constexpr int UG = (P == 4) ? 2 : 1;
             uint32_t Pb[2][P][NQT][2];      // probabilities as B fragments (fp16), per unit and field
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                float S[P][NQT][4];
+            for (int ug = 0; ug < 2 / UG; ++ug) {
+                float S[UG][P][NQT][4];
 #pragma unroll
-                for (int j = 0; j < P; ++j)
+                for (int uu = 0; uu < UG; ++uu)
 #pragma unroll
-                    for (int nq = 0; nq < NQT; ++nq)
+                    for (int j = 0; j < P; ++j)
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) S[j][nq][e] = 0.f;
+                        for (int nq = 0; nq < NQT; ++nq)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) S[uu][j][nq][e] = 0.f;
 #pragma unroll
                 for (int a = 0; a < 4; ++a) {
                     // q * scale for the token groups of this block, channels 32a + 8l .. +7
@@ -544,48 +569,52 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                             qs[gk][nq][3] = hmul2_u32(qr[nq][a][3], s3);
                         }
                     }
-                    uint32_t wl[4], wh[4];
-                    const uint32_t base = kcode + (a >> 1) * 4096 + u * 2048 + k_row_off + k_chunk_off[a & 1];
-                    lds128(base, wl[0], wl[1], wl[2], wl[3]);
-                    lds128(base + 1024, wh[0], wh[1], wh[2], wh[3]);
-                    uint32_t wls[4], whs[4];
 #pragma unroll
-                    for (int x = 0; x < 4; ++x) { wls[x] = wl[x] >> SHIFT; whs[x] = wh[x] >> SHIFT; }
-                    // all fields first, then the MMAs of the first k-slice, then of the second:
-                    // consecutive MMAs never share an accumulator
-                    uint32_t F[P][8];
-                    auto extract = [&](auto jc) {
-                        constexpr int J = decltype(jc)::value;
+                    for (int uu = 0; uu < UG; ++uu) {
+                        const int u = ug * UG + uu;
+                        uint32_t wl[4], wh[4];
+                        const uint32_t base = kcode + (a >> 1) * 4096 + u * 2048 + k_row_off + k_chunk_off[a & 1];
+                        lds128(base, wl[0], wl[1], wl[2], wl[3]);
+                        lds128(base + 1024, wh[0], wh[1], wh[2], wh[3]);
+                        uint32_t wls[4], whs[4];
 #pragma unroll
-                        for (int x = 0; x < 4; ++x) {
-                            F[J][2 * x] = field<BITS, J>(wl[x], wls[x]);
-                            F[J][2 * x + 1] = field<BITS, J>(wh[x], whs[x]);
+                        for (int x = 0; x < 4; ++x) { wls[x] = aux_word<BITS>(wl[x]); whs[x] = aux_word<BITS>(wh[x]); }
+                        // all fields first, then the MMAs of the first k-slice, then of the second:
+                        // consecutive MMAs never share an accumulator
+                        uint32_t F[P][8];
+                        auto extract = [&](auto jc) {
+                            constexpr int J = decltype(jc)::value;
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) {
+                                F[J][2 * x] = field<BITS, J>(wl[x], wls[x]);
+                                F[J][2 * x + 1] = field<BITS, J>(wh[x], whs[x]);
+                            }
+                        };
+                        extract(std::integral_constant<int, 0>{});
+                        extract(std::integral_constant<int, 1>{});
+                        extract(std::integral_constant<int, 2>{});
+                        extract(std::integral_constant<int, 3>{});
+                        if constexpr (P == 8) {
+                            extract(std::integral_constant<int, 4>{});
+                            extract(std::integral_constant<int, 5>{});
+                            extract(std::integral_constant<int, 6>{});
+                            extract(std::integral_constant<int, 7>{});
                         }
-                    };
-                    extract(std::integral_constant<int, 0>{});
-                    extract(std::integral_constant<int, 1>{});
-                    extract(std::integral_constant<int, 2>{});
-                    extract(std::integral_constant<int, 3>{});
-                    if constexpr (P == 8) {
-                        extract(std::integral_constant<int, 4>{});
-                        extract(std::integral_constant<int, 5>{});
-                        extract(std::integral_constant<int, 6>{});
-                        extract(std::integral_constant<int, 7>{});
+#pragma unroll
+                        for (int half = 0; half < 2; ++half)
+#pragma unroll
+                            for (int j = 0; j < P; ++j)
+#pragma unroll
+                                for (int nq = 0; nq < NQT; ++nq)
+                                    mma_f16(S[uu][j][nq], F[j][4 * half], F[j][4 * half + 1], F[j][4 * half + 2],
+                                            F[j][4 * half + 3], qs[j / FPG][nq][2 * half], qs[j / FPG][nq][2 * half + 1]);
                     }
-#pragma unroll
-                    for (int half = 0; half < 2; ++half)
-#pragma unroll
-                        for (int j = 0; j < P; ++j)
-#pragma unroll
-                            for (int nq = 0; nq < NQT; ++nq)
-                                mma_f16(S[j][nq], F[j][4 * half], F[j][4 * half + 1], F[j][4 * half + 2],
-                                        F[j][4 * half + 3], qs[j / FPG][nq][2 * half], qs[j / FPG][nq][2 * half + 1]);
                 }
 
-                // ---------------------------------------------- online softmax (this unit)
+                // ---------------------------------------------- online softmax (these units)
 #pragma unroll
                 for (int nq = 0; nq < NQT; ++nq) {
-                    float t[P][4];
+                    float t[UG * P][4];
                     float zm[NGK][2];       // q.zero term minus the running max of the column
 #pragma unroll
                     for (int gk = 0; gk < NGK; ++gk)
@@ -593,37 +622,51 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                         for (int c = 0; c < 2; ++c)
                             zm[gk][c] = Zc[gk][nq][c] - (m_run[nq][c] == -INFINITY ? 0.f : m_run[nq][c]);
 #pragma unroll
-                    for (int j = 0; j < P; ++j)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) t[j][e] = fmaf(S[j][nq][e], mjs[j], zm[j / FPG][e & 1]);
-                    if (need_mask) {
+                    for (int uu = 0; uu < UG; ++uu)
 #pragma unroll
                         for (int j = 0; j < P; ++j)
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
-                                const int tok = blk * NB + 16 * u + 32 * j + g + 8 * (e >> 1);
-                                if (tok >= seqlen) t[j][e] = -INFINITY;
+                                float sv = S[uu][j][nq][e];
+                                if constexpr (kFieldPairs<BITS>) {
+                                    if ((j & 1) == 0) sv -= S[uu][j + 1][nq][e];   // pair sum minus the odd field
+                                }
+                                t[uu * P + j][e] = fmaf(sv, mjs[j], zm[j / FPG][e & 1]);
                             }
+                    if (need_mask) {
+#pragma unroll
+                        for (int uu = 0; uu < UG; ++uu)
+#pragma unroll
+                            for (int j = 0; j < P; ++j)
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const int tok = blk * NB + 16 * (ug * UG + uu) + 32 * j + g + 8 * (e >> 1);
+                                    if (tok >= seqlen) t[uu * P + j][e] = -INFINITY;
+                                }
                     }
                     float f[2];
-                    if (softmax_step<P, (NGD > 1)>(t, m_run[nq], l_run[nq], O[nq], ZS[nq], f) && u == 1) {
-                        // The first unit's probabilities are still waiting (as B fragments,
+                    if (softmax_step<UG * P, (NGD > 1)>(t, m_run[nq], l_run[nq], O[nq], ZS[nq], f) && ug > 0) {
+                        // The earlier units' probabilities are still waiting (as B fragments,
                         // column = g) for the V phase: bring them to the new maximum too.
                         const float f0 = __shfl_sync(0xffffffffu, f[0], g >> 1);
                         const float f1 = __shfl_sync(0xffffffffu, f[1], g >> 1);
                         const float fq = (g & 1) ? f1 : f0;
                         const uint32_t fh = pack_f16x2(fq, fq);
 #pragma unroll
-                        for (int j = 0; j < P; ++j) {
-                            Pb[0][j][nq][0] = hmul2_u32(Pb[0][j][nq][0], fh);
-                            Pb[0][j][nq][1] = hmul2_u32(Pb[0][j][nq][1], fh);
-                        }
+                        for (int up = 0; up < ug * UG; ++up)
+#pragma unroll
+                            for (int j = 0; j < P; ++j) {
+                                Pb[up][j][nq][0] = hmul2_u32(Pb[up][j][nq][0], fh);
+                                Pb[up][j][nq][1] = hmul2_u32(Pb[up][j][nq][1], fh);
+                            }
                     }
 #pragma unroll
-                    for (int j = 0; j < P; ++j) {
-                        Pb[u][j][nq][0] = movmatrix_trans(pack_f16x2(t[j][0], t[j][1]));
-                        Pb[u][j][nq][1] = movmatrix_trans(pack_f16x2(t[j][2], t[j][3]));
-                    }
+                    for (int uu = 0; uu < UG; ++uu)
+#pragma unroll
+                        for (int j = 0; j < P; ++j) {
+                            Pb[ug * UG + uu][j][nq][0] = movmatrix_trans(pack_f16x2(t[uu * P + j][0], t[uu * P + j][1]));
+                            Pb[ug * UG + uu][j][nq][1] = movmatrix_trans(pack_f16x2(t[uu * P + j][2], t[uu * P + j][3]));
+                        }
                 }
             }
             // K tile consumed: refill it with the next block's K while V is processed
@@ -678,7 +721,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                     for (int cb = 0; cb < NCB; ++cb) {
                         uint32_t r0w, r1w, r2w, r3w;
                         ldsm_x4_trans(vcode + T0 * (DP * 2) + v_off[cb], r0w, r1w, r2w, r3w);
-                        const uint32_t s0w = r0w >> SHIFT, s1w = r1w >> SHIFT, s2w = r2w >> SHIFT, s3w = r3w >> SHIFT;
+                        const uint32_t s0w = aux_word<BITS>(r0w), s1w = aux_word<BITS>(r1w), s2w = aux_word<BITS>(r2w), s3w = aux_word<BITS>(r3w);
                         auto do_vfield = [&](auto jc) {
                             constexpr int JV = decltype(jc)::value;
                             constexpr int gd = JV / FPGV;
@@ -728,8 +771,13 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                 const float wgt = 1.0f / field_weight<BITS>(jv);
                 const int gd = jv / FPGV;
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    acc[(nq * 8 + mt) * 4 + e] = fmaf(O[nq][mt][e], wgt, ZS[nq][(gd == 0 ? 0 : 2) + (e & 1)]);
+                for (int e = 0; e < 4; ++e) {
+                    float ov = O[nq][mt][e];
+                    if constexpr (kFieldPairs<BITS>) {
+                        if ((mt & 1) == 0) ov -= O[nq][mt + 1][e];      // pair sum minus the odd field
+                    }
+                    acc[(nq * 8 + mt) * 4 + e] = fmaf(ov, wgt, ZS[nq][(gd == 0 ? 0 : 2) + (e & 1)]);
+                }
             }
 #pragma unroll
             for (int c = 0; c < 2; ++c) {

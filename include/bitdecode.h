@@ -181,7 +181,8 @@ size_t bd_noalloc_scratch_bytes(void);
  * into this many equal ranges ("rows"), one CTA per (row, KV head), so the grid
  * fills every SM with `ctas_per_sm` resident CTAs of equal work whatever the
  * batch size and lengths.  A caller-given num_splits > 0 asks for
- * num_splits * b rows instead.  `ctas_per_sm` <= 0 selects the default (3).
+ * num_splits * b rows instead.  `ctas_per_sm` <= 0 selects what the decode kernel of this build
+ * keeps resident (one CTA of up to twelve streaming warps per SM).
  */
 int bd_plan_splits(int b, int h_k, int64_t max_s, int bits, int sm_count, int ctas_per_sm);
 
