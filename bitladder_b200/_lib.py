@@ -105,7 +105,7 @@ def load():
     lib.bd_combine.restype = C.c_int
     lib.bd_partition_segments.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
     lib.bd_partition_segments.restype = C.c_int
-    lib.bd_partition_parts.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
+    lib.bd_partition_parts.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
     lib.bd_partition_parts.restype = C.c_int
     lib.bd_read_status.argtypes = [C.c_void_p, C.c_void_p]
     lib.bd_read_status.restype = C.c_int

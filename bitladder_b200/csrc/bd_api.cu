@@ -90,7 +90,8 @@ bool config_supported(int bits, int group, int d) {
 struct DecodePlan {
     int rows;                 // R: ranges the block list of one KV head is cut into
     bool ragged;
-    size_t off_counters, off_table, off_part_out, off_part_lse, total_bytes;
+    int32_t n_uniform;        // units per sequence when the batch is not ragged
+    size_t off_counters, off_table, off_part_out, off_part_lse, off_warp_acc, total_bytes;
 };
 
 inline size_t align16(size_t x) { return (x + 15) & ~size_t(15); }
@@ -116,12 +117,14 @@ int make_plan(const bd_decode_args *a, int sm_count, DecodePlan &plan) {
     const int gq = a->h / a->h_k;
     int64_t rows;
     if (a->num_splits > 0) {
-        rows = std::min<int64_t>(int64_t(a->num_splits) * a->b, std::max<int64_t>(1, int64_t(a->b) * nblk));
+        rows = std::min<int64_t>(int64_t(a->num_splits) * a->b, std::max<int64_t>(1, int64_t(a->b) * (nblk + 4)));
     } else {
         rows = plan_rows(a->b, a->h_k, a->s, a->bits, sm_count, bd::decode_ctas_per_sm(a->bits, a->group, gq));
     }
     plan.rows = int(std::max<int64_t>(1, std::min<int64_t>(rows, 1 << 20)));
-    plan.ragged = a->cache_seqlens != nullptr;
+    const bool has_tail = a->k_res != nullptr;
+    plan.ragged = a->cache_seqlens != nullptr || (has_tail && a->res_lens != nullptr);
+    plan.n_uniform = bd::seq_blocks(a->s, a->s, nb) + (has_tail ? bd::tail_chunks(a->res_len) : 0);
     const size_t slots = (size_t(plan.rows) + a->b) * a->h_k;
     size_t off = 16;                                  // status word
     plan.off_counters = off;
@@ -130,6 +133,8 @@ int make_plan(const bd_decode_args *a, int sm_count, DecodePlan &plan) {
     if (plan.ragged) off = align16(off + (size_t(a->b) + 1) * 2 * sizeof(int32_t));
     plan.off_part_out = off; off += slots * gq * 128 * sizeof(float);
     plan.off_part_lse = off; off = align16(off + slots * gq * sizeof(float));
+    plan.off_warp_acc = off;
+    off = align16(off + size_t(a->b) * a->h_k * bd::decode_deposit_floats(a->bits, a->group, gq) * sizeof(float));
     plan.total_bytes = off;
     return BD_OK;
 }
@@ -221,19 +226,18 @@ int bd_partition_segments(const int32_t *table, int b, int n_uniform, int rows, 
     int n = 0;
     while (walk.next(sg)) {
         if (n < max_segments) {
-            out[4 * n] = sg.ib; out[4 * n + 1] = sg.u0; out[4 * n + 2] = sg.u1; out[4 * n + 3] = sg.owns_tail ? 1 : 0;
+            out[4 * n] = sg.ib; out[4 * n + 1] = sg.u0; out[4 * n + 2] = sg.u1; out[4 * n + 3] = sg.owns_empty ? 1 : 0;
         }
         ++n;
     }
     return n;
 }
 
-int bd_partition_parts(const int32_t *table, int b, int n_uniform, int rows, int ib, int has_tail,
-                       int32_t *out, int max_parts) {
+int bd_partition_parts(const int32_t *table, int b, int n_uniform, int rows, int ib, int32_t *out, int max_parts) {
     if (b <= 0 || rows <= 0 || ib < 0 || ib >= b || !out || max_parts < 0) return BD_ERR_INVALID;
     bd::Partition pt{table, b, n_uniform, rows};
     int n = 0;
-    bd::for_each_part(pt, ib, has_tail != 0, [&](int c) {
+    bd::for_each_part(pt, ib, [&](int c) {
         if (n < max_parts) out[n] = c;
         ++n;
     });
@@ -343,13 +347,15 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     bd::Partition part;
     part.table = plan.ragged ? reinterpret_cast<const int32_t *>(ws + plan.off_table) : nullptr;
     part.b = a->b;
-    part.n_uniform = int32_t((int64_t(a->s) + nb - 1) / nb);
+    part.n_uniform = plan.n_uniform;
     part.R = plan.rows;
 
     cudaError_t err;
     if (plan.ragged) {
         bd::PrefixParams pp;
         pp.cache_seqlens = a->cache_seqlens;
+        pp.res_lens = a->k_res ? a->res_lens : nullptr;
+        pp.res_len = a->k_res ? a->res_len : 0;
         pp.table = reinterpret_cast<int32_t *>(ws + plan.off_table);
         pp.b = a->b; pp.s = a->s; pp.block_tokens = nb;
         err = bd::launch_prefix(pp, stream);
@@ -379,6 +385,7 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     p.part = part;
     // workspace: [status word, 16 B][arrival counters][sequence table][segment partials]
     p.counters = reinterpret_cast<int32_t *>(ws + plan.off_counters);
+    p.warp_acc = reinterpret_cast<float *>(ws + plan.off_warp_acc);
     p.out = a->out; p.lse = a->lse;
     p.out_stride_b = a->out_stride_b; p.out_stride_h = a->out_stride_h;
     p.out_dtype = a->out_dtype;

@@ -55,7 +55,6 @@ namespace bd {
 // warps of the CTA that was launched first and the others finished up to 40 % later.
 constexpr int kMaxWarps = BD_MAX_WARPS;
 constexpr int kSmemLimit = 232448;     // 227 KB of shared memory per CTA
-constexpr int kTailMax = 256;          // longest unquantized tail the kernel accepts
 constexpr float kRescaleSlack = 8.0f;  // keep a stale row max until it is exceeded by 2^8
 
 template <int BITS, int GROUP, int NQT>
@@ -74,17 +73,19 @@ struct Cfg {
     static constexpr int NACC = 8 * NQT * 4 + 4 * NQT;  // floats per thread handed over in a merge
     // per warp: one K tile and one V tile, then their scales/zeros
     static constexpr int WARP_BYTES = 2 * CODE_BYTES + 2 * PRM_BYTES + 16;
-    static constexpr int FIT = (kSmemLimit - NACC * 32 * 4 - 16) / WARP_BYTES;
+    static constexpr int FIT = (kSmemLimit - 32) / (WARP_BYTES + 4);
     // two query tiles need more than 168 registers per thread: eight warps leave 255
     static constexpr int CAP = NQT == 1 ? kMaxWarps : (kMaxWarps < 8 ? kMaxWarps : 8);
     static constexpr int WARPS = FIT < CAP ? FIT : CAP;
     static constexpr int THREADS = WARPS * 32;
     static constexpr size_t OFF_PRM = size_t(WARPS) * 2 * CODE_BYTES;
-    static constexpr size_t OFF_XCHG = OFF_PRM + size_t(WARPS) * 2 * PRM_BYTES;
-    static constexpr size_t OFF_BAR = OFF_XCHG + size_t(NACC) * 32 * 4;
-    static constexpr size_t SMEM = OFF_BAR + 2 * WARPS * 8 + 16;
+    static constexpr size_t OFF_BAR = OFF_PRM + size_t(WARPS) * 2 * PRM_BYTES;
+    static constexpr size_t OFF_FLAGS = OFF_BAR + 2 * WARPS * 8;            // abort flag, then arrivals[WARPS]
+    static constexpr size_t SMEM = OFF_FLAGS + 16 + WARPS * 4;
+    static constexpr int DEPOSIT_FLOATS = NACC * 32;                        // one warp's share of a segment
+    static_assert(DEPOSIT_FLOATS * 4 <= 2 * CODE_BYTES, "a deposit fits the warp's own tile slots");
     static constexpr int CTAS_PER_SM = (SMEM + 1024) * 3 <= 233472 ? 3 : ((SMEM + 1024) * 2 <= 233472 ? 2 : 1);
-    static_assert(WARPS >= 2 && WARPS <= 14, "named barriers 1..WARPS");
+    static_assert(WARPS >= 1 && WARPS <= 32, "one mask bit per warp");
     static_assert(SMEM <= size_t(kSmemLimit), "shared memory");
 };
 
@@ -138,13 +139,6 @@ __host__ __device__ constexpr float field_weight(int j) {
 #else
     return f;
 #endif
-}
-
-__device__ __forceinline__ void bar_sync(int id, int count) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-__device__ __forceinline__ void bar_arrive(int id, int count) {
-    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
 // One online-softmax step for NT score tiles (m16n8 accumulators, columns = query
@@ -206,37 +200,34 @@ __device__ __forceinline__ bool softmax_step(float (&t)[NT][4], float (&m_run)[2
     return any;
 }
 
-// This warp's position in its stream of pack blocks.  The blocks of a row are dealt to
-// the warps round-robin, and the deal continues across the row's segments (`rot` is the
-// warp that gets the first block of the current segment), so that the warps' block
-// counts differ by at most one over the whole row.
-template <int WARPS>
+// This warp's position in its stream of pack blocks: walks the segments of the warp's
+// row and, inside a segment, its pack blocks in order (tail chunks, the units behind a
+// sequence's blocks, are not copied by TMA and are skipped here).
 struct BlockCursor {
     SegWalk walk;
     Segment sg;
-    int32_t u;
-    int32_t rot;
+    const int32_t *cache_seqlens;
+    int32_t s, block_tokens;
+    int32_t u, uend;
     bool valid;
 
-    __device__ __forceinline__ bool seek(int warp) {
+    __device__ __forceinline__ bool seek() {
         while (walk.next(sg)) {
-            int off = warp - rot;
-            if (off < 0) off += WARPS;
-            u = sg.u0 + off;
-            if (sg.u1 > sg.u0) rot = (rot + (sg.u1 - sg.u0)) % WARPS;
-            if (u < sg.u1) return true;
+            const int32_t nblk = seq_blocks(cache_seqlens ? cache_seqlens[sg.ib] : s, s, block_tokens);
+            u = sg.u0;
+            uend = sg.u1 < nblk ? sg.u1 : nblk;
+            if (u < uend) return true;
         }
         return false;
     }
-    __device__ __forceinline__ void init(const Partition &pt, int row, int warp) {
+    __device__ __forceinline__ void init(const Partition &pt, int row, const int32_t *cs, int32_t s_, int32_t nb) {
         walk.init(pt, row);
-        rot = 0;
-        valid = seek(warp);
+        cache_seqlens = cs; s = s_; block_tokens = nb;
+        valid = seek();
     }
-    __device__ __forceinline__ void advance(int warp) {
-        u += WARPS;
-        if (u < sg.u1) return;
-        valid = seek(warp);
+    __device__ __forceinline__ void advance() {
+        if (++u < uend) return;
+        valid = seek();
     }
 };
 
@@ -253,8 +244,8 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     // starts at the beginning of the CTA's window, which is, and the kernel checks it.
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t smem_base = smem_u32(smem);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + C::OFF_BAR + 2 * kWarps * 8);
-    float *xchg = reinterpret_cast<float *>(smem + C::OFF_XCHG);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + C::OFF_FLAGS);
+    int *arrivals = reinterpret_cast<int *>(smem + C::OFF_FLAGS + 16);     // per first sharing warp of a segment
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #ifdef BD_EXP_ROTHEAD
@@ -280,13 +271,16 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
         mbar_init(kbar, 1);
         mbar_init(vbar, 1);
         if (warp == 0) *abort_flag = 0;
+        arrivals[warp] = 0;
         fence_mbar_init();
         tma_prefetch_desc(&kmap);
         tma_prefetch_desc(&vmap);
     }
     __syncthreads();
-    // hand-over buffer starts free: warp 0 holds the credit that warp 3 consumes
-    if (warp == 0) bar_arrive(kWarps, 64);
+    // The warps are the rows of the partition with kWarps times the CTA rows.
+    Partition wpart = p.part;
+    wpart.R = p.part.R * kWarps;
+    const int wrow = row * kWarps + warp;
 
     // ---- TMA issue (one lane) ------------------------------------------------
     auto issue_k = [&](int ib, int blk) {
@@ -310,13 +304,13 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     };
 
     // ---- prologue: first block of this warp ------------------------------------
-    BlockCursor<kWarps> ld;
-    ld.init(p.part, row, warp);
+    BlockCursor ld;
+    ld.init(wpart, wrow, p.cache_seqlens, p.s, NB);
     if (ld.valid && lane == 0) {
         issue_k(ld.sg.ib, ld.u);
         issue_v(ld.sg.ib, ld.u);
     }
-    if (ld.valid) ld.advance(warp);
+    if (ld.valid) ld.advance();
 
     // thread-constant shared-memory offsets
     // K tile: two halves of 64 channels, each [32 pack rows][128 B] with the 128-byte
@@ -342,23 +336,14 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     bool aborted = false;
 
     SegWalk walk;
-    walk.init(p.part, row);
+    walk.init(wpart, wrow);
     Segment sg;
-    int rot = 0;           // warp that takes the first block of the segment (see BlockCursor)
     while (walk.next(sg)) {
         const int ib = sg.ib;
-        int first_off = warp - rot;
-        if (first_off < 0) first_off += kWarps;
-        if (sg.u1 > sg.u0) rot = (rot + (sg.u1 - sg.u0)) % kWarps;
-        int res_n = 0;                                // tail tokens this row owns for this sequence
-        if (sg.owns_tail && p.k_res != nullptr) {
-            res_n = p.res_lens ? p.res_lens[ib] : p.res_len;
-            res_n = min(max(res_n, 0), kTailMax);
-        }
-        if (sg.u1 <= sg.u0 && res_n == 0) {
-            // Nothing of this sequence to stream here.  If it has no tokens at all, the row
-            // that owns its (empty) tail writes the defined result: out = 0, lse = -inf.
-            if (sg.owns_tail && p.part.count(ib) == 0 && warp == 0) {
+        if (sg.u1 <= sg.u0) {
+            // A sequence without any token, answered for by this warp: the defined result is
+            // out = 0, lse = -inf.
+            if (sg.owns_empty) {
                 for (int qrow = 0; qrow < p.gq; ++qrow) {
                     const int64_t hq = int64_t(ih) * p.gq + qrow;
                     const int64_t oi = ib * p.out_stride_b + hq * p.out_stride_h + 4 * lane;
@@ -374,6 +359,12 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
         }
         int seqlen = p.s;
         if (p.cache_seqlens) seqlen = min(max(p.cache_seqlens[ib], 0), p.s);
+        int res_n = 0;                                // tail tokens of this sequence
+        if (p.k_res != nullptr) res_n = min(max(p.res_lens ? p.res_lens[ib] : p.res_len, 0), kTailMax);
+        // this warp's units of the sequence: pack blocks [blk0, blk1), tail tokens [tail0, tail1)
+        const int nblk = (seqlen + NB - 1) / NB;
+        const int blk0 = sg.u0, blk1 = min(sg.u1, nblk);
+        const int tail0 = max(sg.u0 - nblk, 0) * kTailChunk, tail1 = min(max(sg.u1 - nblk, 0) * kTailChunk, res_n);
 
         // Query rows as B fragments: thread (g, l) holds q[row g][32a + 8l .. +7], a = 0..3.
         uint32_t qr[NQT][4][4];
@@ -417,7 +408,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
         // transposed in registers (movmatrix); same running state as the packed
         // blocks, done first so that its loads overlap the TMA copies in flight.
         // ------------------------------------------------------------------
-        for (int tok0 = 16 * warp; tok0 < res_n; tok0 += 16 * kWarps) {
+        for (int tok0 = tail0; tok0 < tail1; tok0 += 16) {
             const int tA = tok0 + g, tB = tA + 8;
             const bool okA = tA < res_n, okB = tB < res_n;
             // rows past the end are read from the last valid row (in bounds) and zeroed afterwards,
@@ -501,7 +492,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             }
         }
 
-        for (int blk = sg.u0 + first_off; blk < sg.u1 && !aborted; blk += kWarps) {
+        for (int blk = blk0; blk < blk1 && !aborted; ++blk) {
             const bool need_mask = (blk + 1) * NB > seqlen;
 
             // ------------------------------------------------------------ K phase
@@ -752,15 +743,22 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                     fence_proxy_async();
                     issue_v(ld.sg.ib, ld.u);
                 }
-                ld.advance(warp);
+                ld.advance();
             }
             phase ^= 1;
         }
         if (aborted) *abort_flag = 1;
 
         // ------------------------------------------------------------------
-        // merge the four warps' partials of this segment: 3 -> 2 -> 1 -> 0, each step
-        // through the hand-over buffer (same register layout on both sides)
+        // End of this warp's share of the sequence.  The warps of the CTA whose ranges
+        // hold units of it each deposit their partial (O, m, l in the fragment layout, the
+        // same in every warp) and count in; no warp waits for another.  The one that counts
+        // in last merges the deposits in warp order (so the result does not depend on who
+        // was last) and finishes the segment.  A warp whose range ends inside the sequence
+        // has nothing left to stream and deposits into its own tile slots in shared memory;
+        // the one warp in whose range the sequence ends goes on with the next sequence, its
+        // tile slots already receive those blocks, and its deposit goes through global
+        // memory (at most one such deposit per sequence and KV head).
         // ------------------------------------------------------------------
         float acc[NACC];       // O in final units (field weights and zero sums applied), then m, l
 #pragma unroll
@@ -790,54 +788,93 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                 acc[32 * NQT + nq * 4 + 2 + c] = sum;
             }
         }
-        auto merge_in = [&]() {
+        // running (acc) merged with another partial whose element i is src(i)
+        auto merge_from = [&](auto src) {
 #pragma unroll
             for (int nq = 0; nq < NQT; ++nq) {
                 float fa[2], fb[2];
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
-                    const float ma = acc[32 * NQT + nq * 4 + c], mb = xchg[(32 * NQT + nq * 4 + c) * 32 + lane];
+                    const float ma = acc[32 * NQT + nq * 4 + c], mb = src(32 * NQT + nq * 4 + c);
                     const float mn = fmaxf(ma, mb);
                     fa[c] = (ma == -INFINITY) ? 0.f : ex2f(ma - mn);
                     fb[c] = (mb == -INFINITY) ? 0.f : ex2f(mb - mn);
                     acc[32 * NQT + nq * 4 + c] = mn;
                     acc[32 * NQT + nq * 4 + 2 + c] = acc[32 * NQT + nq * 4 + 2 + c] * fa[c] +
-                                                      xchg[(32 * NQT + nq * 4 + 2 + c) * 32 + lane] * fb[c];
+                                                      src(32 * NQT + nq * 4 + 2 + c) * fb[c];
                 }
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     const int idx = nq * 32 + i;
-                    acc[idx] = acc[idx] * fa[i & 1] + xchg[idx * 32 + lane] * fb[i & 1];
+                    acc[idx] = acc[idx] * fa[i & 1] + src(idx) * fb[i & 1];
                 }
             }
         };
-        auto hand_over = [&]() {
+        // Which warps of this CTA share the sequence, and which of them goes on afterwards.
+        const int64_t Tw = wpart.total();
+        const int64_t seq_first = wpart.first(ib), seq_end = seq_first + wpart.count(ib);
+        uint32_t share_mask = 0;
+        int goes_on = -1;
+        {
+            int64_t lo = wpart.row_begin(int64_t(row) * kWarps, Tw);
 #pragma unroll
-            for (int i = 0; i < NACC; ++i) xchg[i * 32 + lane] = acc[i];
-        };
-        // chain: warp kWarps-1 -> ... -> 1 -> 0.  Named barrier w (1 <= w < kWarps) hands the
-        // buffer from warp w to warp w-1; barrier kWarps is the credit "buffer free" that warp 0
-        // returns to the head of the chain.
-        if (warp == kWarps - 1) {
-            bar_sync(kWarps, 64);       // buffer free (warp 0 is done with the previous segment)
-            hand_over();
-            __threadfence_block();
-            bar_arrive(kWarps - 1, 64);
-        } else if (warp > 0) {
-            bar_sync(warp + 1, 64);
-            merge_in();
-            hand_over();
-            __threadfence_block();
-            bar_arrive(warp, 64);
-        } else {
-            bar_sync(1, 64);
-            merge_in();
-            bar_arrive(kWarps, 64);
+            for (int w = 0; w < kWarps; ++w) {
+                const int64_t hi = wpart.row_begin(int64_t(row) * kWarps + w + 1, Tw);
+                if (max(lo, seq_first) < min(hi, seq_end)) {
+                    share_mask |= 1u << w;
+                    if (hi > seq_end) goes_on = w;
+                }
+                lo = hi;
+            }
+        }
+        const int nshare = __popc(share_mask);
+        bool finisher = true;
+        if (nshare > 1) {
+            const bool to_global = goes_on == warp;
+            float *gdep = p.warp_acc + (int64_t(ib) * p.h_k + ih) * C::DEPOSIT_FLOATS;
+            if (to_global) {
+#pragma unroll
+                for (int i = 0; i < NACC; ++i) __stcg(gdep + i * 32 + lane, acc[i]);
+                __threadfence();
+            } else {
+                float *mine = reinterpret_cast<float *>(smem + size_t(warp) * 2 * C::CODE_BYTES);
+#pragma unroll
+                for (int i = 0; i < NACC; ++i) mine[i * 32 + lane] = acc[i];
+                __threadfence_block();
+            }
+            __syncwarp();
+            int old = 0;
+            if (lane == 0) old = atomicAdd(arrivals + (__ffs(share_mask) - 1), 1);
+            old = __shfl_sync(0xffffffffu, old, 0);
+            finisher = old == nshare - 1;
+            if (finisher) {
+                if (goes_on >= 0) __threadfence(); else __threadfence_block();
+                // start from the neutral partial and take the deposits in warp order
+#pragma unroll
+                for (int i = 0; i < 32 * NQT; ++i) acc[i] = 0.f;
+#pragma unroll
+                for (int nq = 0; nq < NQT; ++nq) {
+                    acc[32 * NQT + nq * 4 + 0] = acc[32 * NQT + nq * 4 + 1] = -INFINITY;
+                    acc[32 * NQT + nq * 4 + 2] = acc[32 * NQT + nq * 4 + 3] = 0.f;
+                }
+#pragma unroll 1
+                for (int w = 0; w < kWarps; ++w) {
+                    if (((share_mask >> w) & 1u) == 0) continue;
+                    // generic loads: the deposit is in this CTA's shared memory or (one warp's) in
+                    // global memory, written past L1 and never read before in this launch
+                    const float *dep = (w == goes_on) ? gdep
+                                                      : reinterpret_cast<const float *>(smem + size_t(w) * 2 * C::CODE_BYTES);
+                    float v[NACC];
+#pragma unroll
+                    for (int i = 0; i < NACC; ++i) v[i] = dep[i * 32 + lane];
+                    merge_from([&](int i) { return v[i]; });
+                }
+            }
+        }
+        if (finisher) {
             // How many rows hold a part of this sequence?  One: this is the final result.
             // More: leave a normalised partial; the row that arrives last merges them all.
-            bool seq_tail = false;
-            if (p.k_res != nullptr) seq_tail = (p.res_lens ? p.res_lens[ib] : p.res_len) > 0;
-            const PartRange pr = part_range(p.part, ib, seq_tail);
+            const PartRange pr = part_range(p.part, ib);
             int nparts = pr.c1 - pr.c0 + 1;
             if (!pr.dense) {
                 nparts = 0;
@@ -845,41 +882,57 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             }
             const bool final_here = nparts <= 1;
             const int64_t slot = (int64_t(row) + ib) * p.h_k + ih;
+            // normalise in place, then one straight run of stores per destination kind
+            bool row_ok[NQT][2];
 #pragma unroll
             for (int nq = 0; nq < NQT; ++nq) {
-                float inv[2], lse[2];
+                float inv[2];
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     const float M = acc[32 * NQT + nq * 4 + c], L = acc[32 * NQT + nq * 4 + 2 + c];
                     inv[c] = (L > 0.f) ? 1.0f / L : 0.f;
-                    lse[c] = (L > 0.f) ? fmaf(M, 0.6931471805599453f, logf(L)) : -INFINITY;
+                    const float lse = (L > 0.f) ? fmaf(M, 0.6931471805599453f, logf(L)) : -INFINITY;
                     const int qrow = nq * 8 + 2 * l + c;
-                    if (g == 0 && qrow < p.gq) {
-                        if (!final_here) p.part_lse[slot * p.gq + qrow] = lse[c];
-                        else if (p.lse) p.lse[int64_t(ib) * p.h + int64_t(ih) * p.gq + qrow] = lse[c];
+                    row_ok[nq][c] = qrow < p.gq;
+                    if (g == 0 && row_ok[nq][c]) {
+                        if (!final_here) p.part_lse[slot * p.gq + qrow] = lse;
+                        else if (p.lse) p.lse[int64_t(ib) * p.h + int64_t(ih) * p.gq + qrow] = lse;
                     }
                 }
 #pragma unroll
-                for (int mt = 0; mt < 8; ++mt) {
-                    const int jv = (BITS == 4) ? (mt & 3) : mt;
-                    const int pbase = (BITS == 4) ? 16 * (mt >> 2) : 0;
+                for (int i = 0; i < 32; ++i) acc[nq * 32 + i] *= inv[i & 1];
+            }
+            // element (nq, mt, e) of this thread: query row nq*8 + 2l + (e&1), head dim dim_of(mt, e) + g
+            auto dim_of = [](int mt, int e) {
+                const int jv = (BITS == 4) ? (mt & 3) : mt;
+                const int pbase = (BITS == 4) ? 16 * (mt >> 2) : 0;
+                return pbase + 8 * (e >> 1) + DP * jv;
+            };
+            auto store_rows = [&](auto *base, int64_t row_stride, auto cvt) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int dim = pbase + g + 8 * (e >> 1) + DP * jv;
-                        const int qrow = nq * 8 + 2 * l + (e & 1);
-                        const float o = acc[(nq * 8 + mt) * 4 + e] * inv[e & 1];
-                        if (qrow < p.gq) {
-                            if (!final_here) {
-                                p.part_out[(slot * p.gq + qrow) * kHeadDim + dim] = o;
-                            } else {
-                                const int64_t oi = ib * p.out_stride_b + (int64_t(ih) * p.gq + qrow) * p.out_stride_h + dim;
-                                if (p.out_dtype == BD_FP16) static_cast<__half *>(p.out)[oi] = __float2half_rn(o);
-                                else if (p.out_dtype == BD_BF16) static_cast<__nv_bfloat16 *>(p.out)[oi] = __float2bfloat16_rn(o);
-                                else static_cast<float *>(p.out)[oi] = o;
-                            }
-                        }
+                for (int nq = 0; nq < NQT; ++nq)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        if (!row_ok[nq][c]) continue;
+                        auto *rp = base + (nq * 8 + c) * row_stride;
+#pragma unroll
+                        for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+                            for (int eh = 0; eh < 2; ++eh)
+                                rp[dim_of(mt, 2 * eh + c)] = cvt(acc[(nq * 8 + mt) * 4 + 2 * eh + c]);
                     }
-                }
+            };
+            if (!final_here) {
+                store_rows(p.part_out + (slot * p.gq + 2 * l) * kHeadDim + g, int64_t(kHeadDim), [](float x) { return x; });
+            } else {
+                const int64_t o0 = ib * p.out_stride_b + (int64_t(ih) * p.gq + 2 * l) * p.out_stride_h + g;
+                if (p.out_dtype == BD_FP16)
+                    store_rows(static_cast<__half *>(p.out) + o0, p.out_stride_h, [](float x) { return __float2half_rn(x); });
+                else if (p.out_dtype == BD_BF16)
+                    store_rows(static_cast<__nv_bfloat16 *>(p.out) + o0, p.out_stride_h,
+                               [](float x) { return __float2bfloat16_rn(x); });
+                else
+                    store_rows(static_cast<float *>(p.out) + o0, p.out_stride_h, [](float x) { return x; });
             }
             if (!final_here) {
                 // publish the partial, count arrivals; the last one merges (same arithmetic as
@@ -987,8 +1040,8 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                 }
             }
         }
-        // a warp that gave up keeps walking the segments (without streaming) so that
-        // the other warps never wait for it in a merge
+        // a warp that gave up keeps walking its segments (without streaming) and keeps
+        // counting in, so that every segment still finds its last arrival
     }
 
     // ======================================================================
@@ -1015,10 +1068,11 @@ __global__ void __launch_bounds__(256) bd_prefix_kernel(const PrefixParams p) {
     const int per = (p.b + 255) / 256;
     const int lo = min(tid * per, p.b), hi = min(lo + per, p.b);
     int32_t sum = 0;
-    for (int i = lo; i < hi; ++i) {
-        const int32_t len = min(max(p.cache_seqlens[i], 0), p.s);
-        sum += (len + p.block_tokens - 1) / p.block_tokens;
-    }
+    auto units = [&](int i) {
+        return seq_blocks(p.cache_seqlens ? p.cache_seqlens[i] : p.s, p.s, p.block_tokens) +
+               tail_chunks(p.res_lens ? p.res_lens[i] : p.res_len);
+    };
+    for (int i = lo; i < hi; ++i) sum += units(i);
     partial[tid] = sum;
     __syncthreads();
     if (tid == 0) {
@@ -1030,8 +1084,7 @@ __global__ void __launch_bounds__(256) bd_prefix_kernel(const PrefixParams p) {
     __syncthreads();
     int32_t run = partial[tid];
     for (int i = lo; i < hi; ++i) {
-        const int32_t len = min(max(p.cache_seqlens[i], 0), p.s);
-        const int32_t n = (len + p.block_tokens - 1) / p.block_tokens;
+        const int32_t n = units(i);
         p.table[2 * i] = run;
         p.table[2 * i + 1] = n;
         run += n;
@@ -1079,6 +1132,24 @@ cudaError_t launch_decode(const DecodeParams &p, const CUtensorMap &kmap, const 
 cudaError_t launch_prefix(const PrefixParams &p, cudaStream_t stream) {
     bd_prefix_kernel<<<1, 256, 0, stream>>>(p);
     return cudaGetLastError();
+}
+
+#define BD_CFG_PICK(FIELD)                                                                              \
+    const int nqt = gq <= 8 ? 1 : 2;                                                                   \
+    if (bits == 4 && group == 128) return nqt == 1 ? Cfg<4, 128, 1>::FIELD : Cfg<4, 128, 2>::FIELD;     \
+    if (bits == 4 && group == 64) return nqt == 1 ? Cfg<4, 64, 1>::FIELD : Cfg<4, 64, 2>::FIELD;        \
+    if (bits == 2 && group == 128) return nqt == 1 ? Cfg<2, 128, 1>::FIELD : Cfg<2, 128, 2>::FIELD;     \
+    if (bits == 2 && group == 64) return nqt == 1 ? Cfg<2, 64, 1>::FIELD : Cfg<2, 64, 2>::FIELD;
+
+// Streaming warps per CTA of the kernel that serves this configuration.
+int decode_warps(int bits, int group, int gq) {
+    BD_CFG_PICK(WARPS)
+    return 1;
+}
+// Floats of one warp's deposit (its partial of a segment).
+int decode_deposit_floats(int bits, int group, int gq) {
+    BD_CFG_PICK(DEPOSIT_FLOATS)
+    return 0;
 }
 
 int decode_ctas_per_sm(int bits, int group, int gq) {

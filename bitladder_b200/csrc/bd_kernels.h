@@ -30,19 +30,38 @@ struct PackParams {
 // ---------------------------------------------------------------------------
 // Work partition of one decode step.
 //
-// Per KV head, the pack blocks of all sequences form one flat list of T units
-// (sequence 0's blocks, then sequence 1's, ...).  The list is cut into R equal
-// ranges ("rows"); CTA (row c, head ih) streams range c of head ih, so all CTAs
-// carry the same number of blocks (+-1) whatever the batch size and however
-// ragged the lengths are, and the CTAs of one row touch the same tokens of
-// neighbouring heads at the same time.  A range that crosses a sequence boundary
-// yields one partial result per sequence it touches ("segment"); the segment of
-// (row c, sequence ib) owns partial slot c + ib, which is unique because rows and
-// sequences both advance monotonically along the list.  The unquantized tail of a
-// sequence is streamed by the row in which the sequence starts (the last row for
-// empty sequences at the very end) and lands in that row's partial.  The combine
-// kernel walks the same arithmetic to find the parts.
+// A UNIT is one pack block of the quantized cache or one chunk of kTailChunk tokens
+// of the unquantized tail.  Per KV head, the units of all sequences form one flat
+// list of T units (sequence 0's blocks, then its tail chunks, then sequence 1's,
+// ...).  The list is cut into R equal ranges ("rows"); CTA (row c, head ih) streams
+// range c of head ih, so all CTAs carry the same number of units (+-1) whatever the
+// batch size and however ragged the lengths are, and the CTAs of one row touch the
+// same tokens of neighbouring heads at the same time.  Inside the CTA the same cut
+// is applied once more: the warps are the rows of the partition with R * W rows
+// (row c * W + w is warp w of CTA row c; floor(cW * T / (RW)) = floor(c * T / R), so
+// the two levels agree), every warp streams one contiguous range.
+// A range that crosses a sequence boundary yields one partial result per sequence
+// it touches ("segment"); the segment of (CTA row c, sequence ib) owns partial slot
+// c + ib, which is unique because rows and sequences both advance monotonically
+// along the list.  A sequence without any unit is owned by the row whose range
+// holds its position (the last row when it sits behind the last unit); the owner
+// writes the defined result for it.  The merge walks the same arithmetic to find
+// the parts.
 // ---------------------------------------------------------------------------
+constexpr int kTailChunk = 64;    // tokens of the unquantized tail per unit
+constexpr int kTailMax = 256;     // longest unquantized tail the kernel accepts
+
+// Units of one sequence: pack blocks of `len` cached tokens (clamped to the capacity s),
+// then chunks of `res_n` tail tokens.
+BD_HD int32_t seq_blocks(int32_t len, int32_t s, int32_t block_tokens) {
+    len = len < 0 ? 0 : (len > s ? s : len);
+    return (len + block_tokens - 1) / block_tokens;
+}
+BD_HD int32_t tail_chunks(int32_t res_n) {
+    res_n = res_n < 0 ? 0 : (res_n > kTailMax ? kTailMax : res_n);
+    return (res_n + kTailChunk - 1) / kTailChunk;
+}
+
 // Non-negative 64-bit quotient; takes the cheap 32-bit divide when both fit (they
 // almost always do: unit counts and row counts), the emulated one otherwise.
 BD_HD int64_t div_nn(int64_t a, int64_t b) {
@@ -59,16 +78,16 @@ struct Partition {
     BD_HD int64_t first(int ib) const { return table ? int64_t(table[2 * ib]) : int64_t(ib) * n_uniform; }
     BD_HD int32_t count(int ib) const { return table ? table[2 * ib + 1] : n_uniform; }
     // first unit of row c (c == R gives T)
-    BD_HD int64_t row_begin(int c, int64_t T) const { return div_nn(int64_t(c) * T, R); }
+    BD_HD int64_t row_begin(int64_t c, int64_t T) const { return div_nn(c * T, R); }
     // row that holds unit f (0 <= f < T)
     BD_HD int32_t row_of(int64_t f, int64_t T) const { return int32_t(div_nn((f + 1) * R - 1, T)); }
 };
 
-// One segment of a row: units [u0, u1) of sequence ib (u1 <= u0: no pack blocks,
-// the row only owns the sequence's tail).
+// One segment of a row: units [u0, u1) of sequence ib, or (u1 <= u0, owns_empty) a
+// sequence without units that this row answers for.
 struct Segment {
     int32_t ib, u0, u1;
-    bool owns_tail;
+    bool owns_empty;
 };
 
 // Walks the segments of row c in order.  Pure integer arithmetic on the
@@ -83,7 +102,7 @@ struct SegWalk {
         c = row;
         T = p.total();
         f0 = p.row_begin(row, T);
-        f1 = p.row_begin(row + 1, T);
+        f1 = p.row_begin(int64_t(row) + 1, T);
         ib = find_start();
     }
     // smallest ib with first(ib) >= f0 or first(ib) + count(ib) > f0
@@ -110,23 +129,23 @@ struct SegWalk {
             sg.ib = ib;
             sg.u0 = int32_t(lo - fb);
             sg.u1 = int32_t(hi - fb);
-            sg.owns_tail = trailing || (fb >= f0 && fb < f1);
+            sg.owns_empty = n <= 0 && (trailing || (fb >= f0 && fb < f1));
             ++ib;
-            if (sg.u1 > sg.u0 || sg.owns_tail) return true;
+            if (sg.u1 > sg.u0 || sg.owns_empty) return true;
         }
         return false;
     }
 };
 
-// Rows that hold a part of sequence ib (the merge side of the same arithmetic).
-// A sequence without pack blocks but with a tail has one part, in the row that owns
-// its tail.  When every row has blocks (T >= R, the normal case) the parts are the
-// consecutive rows c0 .. c1; with more rows than units some rows in between are empty.
+// Rows that hold a part of sequence ib (the merge side of the same arithmetic); none
+// for a sequence without units.  When every row has units (T >= R, the normal case)
+// the parts are the consecutive rows c0 .. c1; with more rows than units some rows in
+// between are empty.
 struct PartRange {
     int32_t c0, c1;           // inclusive; c1 < c0: no part
     bool dense;               // every row of the range holds a part
 };
-BD_HD PartRange part_range(const Partition &pt, int ib, bool has_tail) {
+BD_HD PartRange part_range(const Partition &pt, int ib) {
     const int64_t T = pt.total();
     const int64_t first = pt.first(ib), n = pt.count(ib);
     PartRange r{0, -1, true};
@@ -134,22 +153,20 @@ BD_HD PartRange part_range(const Partition &pt, int ib, bool has_tail) {
         r.c0 = pt.row_of(first, T);
         r.c1 = pt.row_of(first + n - 1, T);
         r.dense = T >= pt.R;
-    } else if (has_tail) {
-        r.c0 = r.c1 = (T > 0 ? pt.row_of(first < T ? first : T - 1, T) : pt.R - 1);
     }
     return r;
 }
-BD_HD bool row_has_part(const Partition &pt, int ib, int c) {
+BD_HD bool row_has_part(const Partition &pt, int ib, int64_t c) {
     const int64_t T = pt.total();
     const int64_t first = pt.first(ib), n = pt.count(ib);
-    if (n <= 0) return true;                   // the single tail part
+    if (n <= 0) return false;
     const int64_t b0 = pt.row_begin(c, T), b1 = pt.row_begin(c + 1, T);
     const int64_t lo = b0 > first ? b0 : first, hi = b1 < first + n ? b1 : first + n;
     return hi > lo;
 }
 template <class F>
-BD_HD void for_each_part(const Partition &pt, int ib, bool has_tail, F &&f) {
-    const PartRange r = part_range(pt, ib, has_tail);
+BD_HD void for_each_part(const Partition &pt, int ib, F &&f) {
+    const PartRange r = part_range(pt, ib);
     for (int c = r.c0; c <= r.c1; ++c)
         if (r.dense || row_has_part(pt, ib, c)) f(c);
 }
@@ -176,6 +193,7 @@ struct DecodeParams {
     float *part_out;              // [(R + b) * h_k segment slots][gq][128] fp32, normalised
     float *part_lse;              // [(R + b) * h_k][gq]
     int32_t *counters;            // [b * h_k] parts arrived per (sequence, KV head); zero between steps
+    float *warp_acc;              // [b * h_k][deposit floats]: the share of the warp in whose range a sequence ends
     void *out;                    // (b, h, d) final result
     float *lse;                   // optional (b, h)
     int64_t out_stride_b, out_stride_h;
@@ -184,9 +202,10 @@ struct DecodeParams {
 };
 
 struct PrefixParams {
-    const int32_t *cache_seqlens;
+    const int32_t *cache_seqlens;     // null: every sequence has s tokens
+    const int32_t *res_lens;          // null: every sequence has res_len tail tokens
     int32_t *table;
-    int32_t b, s, block_tokens;
+    int32_t b, s, block_tokens, res_len;
 };
 
 struct CombinePartsParams {
@@ -204,6 +223,8 @@ cudaError_t launch_prefix(const PrefixParams &p, cudaStream_t stream);
 cudaError_t launch_decode(const DecodeParams &p, const CUtensorMap &kmap, const CUtensorMap &vmap,
                           int bits, int group, cudaStream_t stream);
 int decode_ctas_per_sm(int bits, int group, int gq);
+int decode_warps(int bits, int group, int gq);
+int decode_deposit_floats(int bits, int group, int gq);
 cudaError_t launch_combine_parts(const CombinePartsParams &p, cudaStream_t stream);
 
 }  // namespace bd

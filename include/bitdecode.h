@@ -188,18 +188,21 @@ int bd_plan_splits(int b, int h_k, int64_t max_s, int bits, int sm_count, int ct
 
 /*
  * Host-side view of that partition, for tests and debugging (pure integer
- * arithmetic, no device work, no counterpart in the reference).  `table` is null
- * for equal lengths (then every sequence has n_uniform pack blocks) or points
- * to HOST memory holding (first block, block count) per sequence followed by
- * (total, 0).  bd_partition_segments writes up to max_segments tuples
- * (sequence, first block, end block, owns_tail) covered by `row`;
- * bd_partition_parts writes the rows that hold a part of sequence `ib`
- * (`has_tail`: the sequence has unquantized tail tokens).
- * Both return the number of entries found.
+ * arithmetic, no device work, no counterpart in the reference).  A unit is one
+ * pack block or one 64-token chunk of the unquantized tail; a sequence's units are
+ * its blocks, then its tail chunks.  `table` is null for equal lengths (then every
+ * sequence has n_uniform units) or points to HOST memory holding (first unit, unit
+ * count) per sequence followed by (total, 0).  bd_partition_segments writes up to
+ * max_segments tuples (sequence, first unit, end unit, owns_empty) covered by
+ * `row`; owns_empty marks a sequence without units that this row answers for.
+ * bd_partition_parts writes the rows that hold a part of sequence `ib` (none for
+ * a sequence without units).  Both return the number of entries found.  The decode
+ * kernel applies the partition twice: `rows` CTAs per KV head, and rows * W warps
+ * (W warps per CTA), warp w of CTA c being row c * W + w.
  */
 int bd_partition_segments(const int32_t *table, int b, int n_uniform, int rows, int row,
                           int32_t *out, int max_segments);
-int bd_partition_parts(const int32_t *table, int b, int n_uniform, int rows, int ib, int has_tail,
+int bd_partition_parts(const int32_t *table, int b, int n_uniform, int rows, int ib,
                        int32_t *out, int max_parts);
 
 /*

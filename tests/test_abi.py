@@ -90,15 +90,17 @@ def _segments(lib, table, b, n, R, row):
 
 def _parts(lib, table, b, n, R, ib):
     out = np.zeros(4096, np.int32)
-    k = lib.bd_partition_parts(None if table is None else table.ctypes.data, b, n, R, ib, 1, out.ctypes.data, 4096)
+    k = lib.bd_partition_parts(None if table is None else table.ctypes.data, b, n, R, ib, out.ctypes.data, 4096)
     assert k >= 0
     return list(out[:k])
 
 
-def test_partition_covers_every_block_once_and_is_balanced():
-    """The arithmetic the decode kernel and its merge share: every pack block belongs to exactly
-    one row, rows differ by at most one block, partial slots (row + sequence) never clash, every
-    sequence's tail has exactly one owner, and the merge finds exactly the rows that wrote."""
+def test_partition_covers_every_unit_once_and_is_balanced():
+    """The arithmetic the decode kernel and its merge share: every unit (pack block or tail
+    chunk) belongs to exactly one row, rows differ by at most one unit, partial slots (row +
+    sequence) never clash, every sequence without units has exactly one row that answers for it,
+    and the merge finds exactly the rows that wrote.  The kernel cuts twice with the same
+    arithmetic (CTAs, then warps inside a CTA): the finer cut must nest inside the coarser."""
     lib = _lib.load()
     rnd = random.Random(7)
     for _ in range(600):
@@ -111,13 +113,14 @@ def test_partition_covers_every_block_once_and_is_balanced():
             firsts = np.cumsum([0] + counts)
             table = np.zeros(2 * (b + 1), np.int32)
             table[0:2 * b:2], table[1:2 * b:2], table[2 * b], n = firsts[:-1], counts, firsts[-1], 0
-        cover, tails, slots = {}, {}, set()
+        cover, empties, slots = {}, {}, set()
         rows_of = {ib: [] for ib in range(b)}
         per_row = []
         for row in range(R):
             tot = 0
             for ib, u0, u1, owns in _segments(lib, table, b, n, R, row):
                 if u1 > u0:
+                    assert not owns
                     assert (row + ib) not in slots
                     slots.add(row + ib)
                     rows_of[ib].append(row)
@@ -125,15 +128,20 @@ def test_partition_covers_every_block_once_and_is_balanced():
                     for u in range(u0, u1):
                         assert (ib, u) not in cover
                         cover[(ib, u)] = row
-                if owns:
-                    assert ib not in tails
-                    tails[ib] = row
+                else:
+                    assert owns and counts[ib] == 0
+                    assert ib not in empties
+                    empties[ib] = row
             per_row.append(tot)
         assert len(cover) == sum(counts)
-        assert set(tails) == set(range(b))
+        assert set(empties) == {ib for ib in range(b) if counts[ib] == 0}
         assert max(per_row) - min(per_row) <= 1
         for ib in range(b):
-            expect = rows_of[ib] if counts[ib] > 0 else [tails[ib]]
-            assert _parts(lib, table, b, n, R, ib) == expect
-            if counts[ib] > 0:
-                assert tails[ib] == rows_of[ib][0]       # the tail rides in the sequence's first part
+            assert _parts(lib, table, b, n, R, ib) == rows_of[ib]
+        # the warp-level cut (W rows per CTA row) nests inside the CTA-level cut
+        W = rnd.choice([2, 8, 12])
+        for row in range(R):
+            coarse = [(ib, u) for ib, u0, u1, _ in _segments(lib, table, b, n, R, row) for u in range(u0, u1)]
+            fine = [(ib, u) for w in range(W) for ib, u0, u1, _ in _segments(lib, table, b, n, R * W, row * W + w)
+                    for u in range(u0, u1)]
+            assert fine == coarse
