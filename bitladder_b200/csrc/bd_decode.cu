@@ -304,7 +304,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     };
 
     // ---- prologue: first block of this warp ------------------------------------
-    BlockCursor ld;
+    BlockCursor ld;                 // next block to copy into this warp's tiles
     ld.init(wpart, wrow, p.cache_seqlens, p.s, NB);
     if (ld.valid && lane == 0) {
         issue_k(ld.sg.ib, ld.u);
@@ -788,28 +788,6 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                 acc[32 * NQT + nq * 4 + 2 + c] = sum;
             }
         }
-        // running (acc) merged with another partial whose element i is src(i)
-        auto merge_from = [&](auto src) {
-#pragma unroll
-            for (int nq = 0; nq < NQT; ++nq) {
-                float fa[2], fb[2];
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    const float ma = acc[32 * NQT + nq * 4 + c], mb = src(32 * NQT + nq * 4 + c);
-                    const float mn = fmaxf(ma, mb);
-                    fa[c] = (ma == -INFINITY) ? 0.f : ex2f(ma - mn);
-                    fb[c] = (mb == -INFINITY) ? 0.f : ex2f(mb - mn);
-                    acc[32 * NQT + nq * 4 + c] = mn;
-                    acc[32 * NQT + nq * 4 + 2 + c] = acc[32 * NQT + nq * 4 + 2 + c] * fa[c] +
-                                                      src(32 * NQT + nq * 4 + 2 + c) * fb[c];
-                }
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int idx = nq * 32 + i;
-                    acc[idx] = acc[idx] * fa[i & 1] + src(idx) * fb[i & 1];
-                }
-            }
-        };
         // Which warps of this CTA share the sequence, and which of them goes on afterwards.
         const int64_t Tw = wpart.total();
         const int64_t seq_first = wpart.first(ib), seq_end = seq_first + wpart.count(ib);
@@ -849,25 +827,54 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             finisher = old == nshare - 1;
             if (finisher) {
                 if (goes_on >= 0) __threadfence(); else __threadfence_block();
-                // start from the neutral partial and take the deposits in warp order
+                // The deposits sit in this CTA's shared memory or (one warp's) in global memory,
+                // written past L1 and never read before in this launch: generic loads serve both.
+                auto deposit_of = [&](int w) {
+                    return (w == goes_on) ? static_cast<const float *>(gdep)
+                                          : reinterpret_cast<const float *>(smem + size_t(w) * 2 * C::CODE_BYTES);
+                };
+                // pass 1: the column maxima over all deposits
+                float mx[NQT][2];
 #pragma unroll
-                for (int i = 0; i < 32 * NQT; ++i) acc[i] = 0.f;
-#pragma unroll
-                for (int nq = 0; nq < NQT; ++nq) {
-                    acc[32 * NQT + nq * 4 + 0] = acc[32 * NQT + nq * 4 + 1] = -INFINITY;
-                    acc[32 * NQT + nq * 4 + 2] = acc[32 * NQT + nq * 4 + 3] = 0.f;
-                }
-#pragma unroll 1
+                for (int nq = 0; nq < NQT; ++nq) mx[nq][0] = mx[nq][1] = -INFINITY;
+#pragma unroll 4
                 for (int w = 0; w < kWarps; ++w) {
                     if (((share_mask >> w) & 1u) == 0) continue;
-                    // generic loads: the deposit is in this CTA's shared memory or (one warp's) in
-                    // global memory, written past L1 and never read before in this launch
-                    const float *dep = (w == goes_on) ? gdep
-                                                      : reinterpret_cast<const float *>(smem + size_t(w) * 2 * C::CODE_BYTES);
+                    const float *dep = deposit_of(w);
+#pragma unroll
+                    for (int nq = 0; nq < NQT; ++nq)
+#pragma unroll
+                        for (int c = 0; c < 2; ++c)
+                            mx[nq][c] = fmaxf(mx[nq][c], dep[(32 * NQT + nq * 4 + c) * 32 + lane]);
+                }
+                // pass 2: the weighted sum in warp order (every term independent of the others
+                // but for the running sums, so the loads and exponentials overlap)
+#pragma unroll
+                for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
+#pragma unroll 2
+                for (int w = 0; w < kWarps; ++w) {
+                    if (((share_mask >> w) & 1u) == 0) continue;
+                    const float *dep = deposit_of(w);
                     float v[NACC];
 #pragma unroll
                     for (int i = 0; i < NACC; ++i) v[i] = dep[i * 32 + lane];
-                    merge_from([&](int i) { return v[i]; });
+#pragma unroll
+                    for (int nq = 0; nq < NQT; ++nq) {
+                        float f[2];
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            const float mw = v[32 * NQT + nq * 4 + c];
+                            f[c] = (mw == -INFINITY) ? 0.f : ex2f(mw - mx[nq][c]);
+                            acc[32 * NQT + nq * 4 + 2 + c] = fmaf(f[c], v[32 * NQT + nq * 4 + 2 + c], acc[32 * NQT + nq * 4 + 2 + c]);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[nq * 32 + i] = fmaf(f[i & 1], v[nq * 32 + i], acc[nq * 32 + i]);
+                    }
+                }
+#pragma unroll
+                for (int nq = 0; nq < NQT; ++nq) {
+                    acc[32 * NQT + nq * 4 + 0] = mx[nq][0];
+                    acc[32 * NQT + nq * 4 + 1] = mx[nq][1];
                 }
             }
         }
@@ -950,6 +957,71 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                     // round independent of the others.
                     const int nrows = pr.c1 - pr.c0 + 1;
                     const int64_t slot0 = (int64_t(pr.c0) + ib) * p.h_k + ih;
+                    // final row `qrow` of this KV head: o holds the weighted sum of this lane's 4 dims
+                    auto write_row = [&](int qrow, float (&o)[4], float mxv, float sumv) {
+                        float lse_f = -INFINITY;
+                        if (mxv != -INFINITY) {
+                            const float inv = 1.0f / sumv;
+                            o[0] *= inv; o[1] *= inv; o[2] *= inv; o[3] *= inv;
+                            lse_f = mxv + logf(sumv);
+                        }
+                        const int64_t hq = int64_t(ih) * p.gq + qrow;
+                        const int64_t oi = ib * p.out_stride_b + hq * p.out_stride_h + 4 * lane;
+                        if (p.out_dtype == BD_FP16) {
+                            __half2 a = __floats2half2_rn(o[0], o[1]), b2 = __floats2half2_rn(o[2], o[3]);
+                            *reinterpret_cast<uint2 *>(static_cast<__half *>(p.out) + oi) =
+                                make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b2));
+                        } else if (p.out_dtype == BD_BF16) {
+                            __nv_bfloat162 a = __floats2bfloat162_rn(o[0], o[1]), b2 = __floats2bfloat162_rn(o[2], o[3]);
+                            *reinterpret_cast<uint2 *>(static_cast<__nv_bfloat16 *>(p.out) + oi) =
+                                make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b2));
+                        } else {
+                            *reinterpret_cast<float4 *>(static_cast<float *>(p.out) + oi) = make_float4(o[0], o[1], o[2], o[3]);
+                        }
+                        if (lane == 0 && p.lse) p.lse[int64_t(ib) * p.h + hq] = lse_f;
+                    };
+                    if (pr.dense && nrows <= 4) {
+                        // The usual case, a sequence cut into a few parts: every load of a round
+                        // (4 query rows x 4 parts: the LSEs and this lane's 16 bytes of each part) is
+                        // issued before any is used, one trip to L2 for all of them.
+#pragma unroll 1
+                        for (int q0 = 0; q0 < p.gq; q0 += 4) {
+                            float ls[4][4];
+                            float4 v[4][4];
+#pragma unroll
+                            for (int jj = 0; jj < 4; ++jj) {
+                                const int64_t sl = slot0 + int64_t(jj) * p.h_k;
+#pragma unroll
+                                for (int qq = 0; qq < 4; ++qq) {
+                                    const bool live = jj < nrows && q0 + qq < p.gq;
+                                    ls[jj][qq] = -INFINITY;
+                                    v[jj][qq] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                    if (live) {
+                                        ls[jj][qq] = __ldcg(p.part_lse + sl * p.gq + q0 + qq);
+                                        v[jj][qq] = __ldcg(reinterpret_cast<const float4 *>(
+                                            p.part_out + (sl * p.gq + q0 + qq) * kHeadDim + 4 * lane));
+                                    }
+                                }
+                            }
+#pragma unroll
+                            for (int qq = 0; qq < 4; ++qq) {
+                                if (q0 + qq >= p.gq) continue;
+                                const float mxv = fmaxf(fmaxf(ls[0][qq], ls[1][qq]), fmaxf(ls[2][qq], ls[3][qq]));
+                                float sumv = 0.f;
+                                float o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                                for (int jj = 0; jj < 4; ++jj) {
+                                    const float wv = (ls[jj][qq] == -INFINITY) ? 0.f : __expf(ls[jj][qq] - mxv);
+                                    sumv += wv;
+                                    if (wv != 0.f) {
+                                        o[0] = fmaf(wv, v[jj][qq].x, o[0]); o[1] = fmaf(wv, v[jj][qq].y, o[1]);
+                                        o[2] = fmaf(wv, v[jj][qq].z, o[2]); o[3] = fmaf(wv, v[jj][qq].w, o[3]);
+                                    }
+                                }
+                                write_row(q0 + qq, o, mxv, sumv);
+                            }
+                        }
+                    } else {
                     for (int q0 = 0; q0 < p.gq; q0 += 4) {
                         // pass 1: lane i reads the LSEs of row c0 + i (32 rows per round); one
                         // round trip to L2 for all of them, then warp reductions
@@ -1010,31 +1082,9 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                             }
                         }
 #pragma unroll
-                        for (int qq = 0; qq < 4; ++qq) {
-                            if (q0 + qq >= p.gq) continue;
-                            float lse_f = -INFINITY;
-                            if (mx[qq] != -INFINITY) {
-                                const float inv = 1.0f / sum[qq];
-                                o[qq][0] *= inv; o[qq][1] *= inv; o[qq][2] *= inv; o[qq][3] *= inv;
-                                lse_f = mx[qq] + logf(sum[qq]);
-                            }
-                            const int64_t hq = int64_t(ih) * p.gq + q0 + qq;
-                            const int64_t oi = ib * p.out_stride_b + hq * p.out_stride_h + 4 * lane;
-                            if (p.out_dtype == BD_FP16) {
-                                __half2 a = __floats2half2_rn(o[qq][0], o[qq][1]), b2 = __floats2half2_rn(o[qq][2], o[qq][3]);
-                                *reinterpret_cast<uint2 *>(static_cast<__half *>(p.out) + oi) =
-                                    make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b2));
-                            } else if (p.out_dtype == BD_BF16) {
-                                __nv_bfloat162 a = __floats2bfloat162_rn(o[qq][0], o[qq][1]),
-                                               b2 = __floats2bfloat162_rn(o[qq][2], o[qq][3]);
-                                *reinterpret_cast<uint2 *>(static_cast<__nv_bfloat16 *>(p.out) + oi) =
-                                    make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b2));
-                            } else {
-                                *reinterpret_cast<float4 *>(static_cast<float *>(p.out) + oi) =
-                                    make_float4(o[qq][0], o[qq][1], o[qq][2], o[qq][3]);
-                            }
-                            if (lane == 0 && p.lse) p.lse[int64_t(ib) * p.h + hq] = lse_f;
-                        }
+                        for (int qq = 0; qq < 4; ++qq)
+                            if (q0 + qq < p.gq) write_row(q0 + qq, o[qq], mx[qq], sum[qq]);
+                    }
                     }
                     if (lane == 0) p.counters[int64_t(ib) * p.h_k + ih] = 0;   // ready for the next step
                 }
