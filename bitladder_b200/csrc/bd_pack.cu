@@ -26,15 +26,20 @@ __device__ __forceinline__ float2 pair_to_float2(uint32_t w) {
     }
 }
 
-// roundf() for v >= 0 (ties away from zero).  v - trunc(v) is exact, so the
-// comparison sees the true fraction; NaN falls through to the clamp like the
-// reference's fmaxf(roundf(NaN), 0) = 0.
+// clamp(roundf(v), 0, maxv) as an integer, v = (x - mn) * scale_inv, without the conversion
+// unit (a quarter-rate pipe that two conversions per element would saturate).
+//   - fmaxf(NaN, 0) = 0 and the clamp to [0, maxv] come first; round(clamp(v)) equals
+//     clamp(round(v)) because both are monotone and the bounds are integers, and it is what
+//     the reference's fminf(fmaxf(roundf(v), 0), maxv) gives for NaN and infinities;
+//   - 2^23 + v added with round-toward-zero is exactly 2^23 + trunc(v) (0 <= v < 2^22): the
+//     integer part sits in the low mantissa bits;
+//   - v - trunc(v) is exact, so the tie test sees the true fraction (roundf: ties away from zero).
 __device__ __forceinline__ uint32_t quant_code(float x, float mn, float scale_inv, float maxv) {
     float v = __fmul_rn(__fsub_rn(x, mn), scale_inv);
-    float r = truncf(v);
-    r = __fadd_rn(r, (__fsub_rn(v, r) >= 0.5f) ? 1.0f : 0.0f);
-    r = fminf(fmaxf(r, 0.0f), maxv);
-    return static_cast<uint32_t>(r);
+    v = fminf(fmaxf(v, 0.0f), maxv);
+    const float t = __fadd_rz(v, 8388608.0f);
+    const float frac = __fsub_rn(v, __fsub_rn(t, 8388608.0f));
+    return (__float_as_uint(t) & 0xffu) + (frac >= 0.5f ? 1u : 0u);
 }
 
 __device__ __forceinline__ void scale_from_minmax(float mn, float mx, float maxv, float &scale_inv, float &scale) {
