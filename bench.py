@@ -138,6 +138,9 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.samples)}
 
 
+NCU_TRAFFIC_C2 = 291_432_192     # bytes per launch: 287.498 MB read + 3.934 MB written
+NCU_ALGO_C2 = 287_440_896        # algorithmic bytes of the same launch
+
 # ---------------------------------------------------------------------------
 # workload construction
 # ---------------------------------------------------------------------------
@@ -412,6 +415,12 @@ def main():
 
     peak, peak_src = measured_peak_gbs()
     achieved = nbytes / (ms_per_step * 1e-3) / 1e9
+    # DRAM bytes (read + write) of one decode launch from the ncu capture summarised in
+    # profiles/decode_kernel_c2_4bit.md; for the other workloads the same ratio to the
+    # algorithmic bytes (every byte is read once, partials add about 1.4 %).
+    traffic = NCU_TRAFFIC_C2 if args.workload == "C2" else round(nbytes * NCU_TRAFFIC_C2 / NCU_ALGO_C2)
+    traffic_src = ("ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch of this workload"
+                   if args.workload == "C2" else "scaled from the C2 capture by algorithmic bytes")
     splits = B.plan_splits(w["b"], w["h_k"], w["s"], w["bits"], torch.cuda.get_device_properties(device).multi_processor_count)
 
     cpu = None
@@ -430,7 +439,7 @@ def main():
                        "rows_per_kv_head": splits, "launch": "cuda graph replay" if graph is not None else "eager",
                        "l2": f"{args.copies} rotating packed-cache copies of {nbytes / 2**20:.0f} MiB each (> 126 MB L2)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src,
+                         "traffic": traffic, "traffic_source": traffic_src, "peak_source": peak_src,
                          "note": "achieved = algorithmic bytes per step / CUDA-event time of the whole step "
                                  "(one split-KV decode kernel launch; the range that finishes last merges the partials)",
                          "algorithmic_bytes_per_step": nbytes},
