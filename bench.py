@@ -265,6 +265,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-preroll", action="store_true", help="skip the half-second clock pre-roll (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--graph-steps", type=int, default=48, help="decode steps held by one CUDA graph")
     ap.add_argument("--eager", action="store_true", help="launch every step from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
@@ -318,6 +319,7 @@ def main():
     # rotating cache copy), so the device is never waiting for the Python caller;
     # steps that do not fill a whole graph are launched eagerly.
     ncopy = len(caches)
+    per_graph = ncopy * max(1, args.graph_steps // ncopy)     # steps held by one graph (whole rotations)
     graph = None
     if not args.eager:
         try:
@@ -326,7 +328,7 @@ def main():
             with torch.cuda.stream(side):
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, stream=side):
-                    for i in range(ncopy):
+                    for i in range(per_graph):
                         step(i)
             torch.cuda.current_stream().wait_stream(side)
         except Exception as exc:   # capture unsupported: fall back to eager launches
@@ -339,12 +341,12 @@ def main():
             for i in range(n):
                 step(i)
             return
-        for _ in range(n // ncopy):
+        for _ in range(n // per_graph):
             graph.replay()
-        for i in range(n % ncopy):
+        for i in range(n % per_graph):
             step(i)
 
-    run_steps(max(ncopy, 3))
+    run_steps(max(per_graph, 3))
     barrier()
 
     sampler = ClockSampler(local_rank)
