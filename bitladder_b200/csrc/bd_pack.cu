@@ -12,6 +12,7 @@
 // The work is pure streaming (read 2*NB*d*2 bytes, write a quarter or an eighth
 // of that): every thread keeps 64 packed pairs in flight for K, rows are read
 // and written in 128-byte warp segments, and nothing is re-read.
+#include <type_traits>
 #include "bd_common.cuh"
 #include "bd_kernels.h"
 
@@ -26,20 +27,23 @@ __device__ __forceinline__ float2 pair_to_float2(uint32_t w) {
     }
 }
 
-// clamp(roundf(v), 0, maxv) as an integer, v = (x - mn) * scale_inv, without the conversion
-// unit (a quarter-rate pipe that two conversions per element would saturate).
-//   - fmaxf(NaN, 0) = 0 and the clamp to [0, maxv] come first; round(clamp(v)) equals
-//     clamp(round(v)) because both are monotone and the bounds are integers, and it is what
-//     the reference's fminf(fmaxf(roundf(v), 0), maxv) gives for NaN and infinities;
-//   - 2^23 + v added with round-toward-zero is exactly 2^23 + trunc(v) (0 <= v < 2^22): the
-//     integer part sits in the low mantissa bits;
-//   - v - trunc(v) is exact, so the tie test sees the true fraction (roundf: ties away from zero).
-__device__ __forceinline__ uint32_t quant_code(float x, float mn, float scale_inv, float maxv) {
-    float v = __fmul_rn(__fsub_rn(x, mn), scale_inv);
-    v = fminf(fmaxf(v, 0.0f), maxv);
-    const float t = __fadd_rz(v, 8388608.0f);
-    const float frac = __fsub_rn(v, __fsub_rn(t, 8388608.0f));
-    return (__float_as_uint(t) & 0xffu) + (frac >= 0.5f ? 1u : 0u);
+// roundf(v) for v = (x - mn) * scale_inv, left in the mantissa of a float: one add.
+//   v lies in [0, maxv + 1e-6] (x >= mn, and (mx - mn) * fl(maxv / (mx - mn)) exceeds maxv by a few
+//   ulps at most), or is NaN (NaN or infinite inputs), which fmaxf turns into 0 exactly like the
+//   reference's fminf(fmaxf(roundf(v), 0), maxv); the clamp from above never acts.
+//   2^22 + 0.5 has an ulp of 0.5, so v + (2^22 + 0.5) rounded toward zero is 2^22 plus
+//   v + 0.5 cut to a multiple of 0.5; cutting the half away too gives floor(v + 0.5), which for
+//   v >= 0 is roundf(v) (ties away from zero).  The integer sits in mantissa bits 1 and up.
+__device__ __forceinline__ uint32_t quant_bits(float x, float mn, float scale_inv) {
+    const float v = fmaxf(__fmul_rn(__fsub_rn(x, mn), scale_inv), 0.0f);
+    return __float_as_uint(__fadd_rz(v, 4194304.5f));
+}
+// acc |= code << (BITS * J), the code taken from quant_bits (one shift, one three-input logic op)
+template <int BITS, int J>
+__device__ __forceinline__ uint32_t put_field(uint32_t acc, uint32_t qbits) {
+    constexpr uint32_t kMask = ((1u << BITS) - 1u) << (BITS * J);
+    if constexpr (BITS * J == 0) return acc | ((qbits >> 1) & kMask);
+    else return acc | ((qbits << (BITS * J - 1)) & kMask);
 }
 
 __device__ __forceinline__ void scale_from_minmax(float mn, float mx, float maxv, float &scale_inv, float &scale) {
@@ -48,8 +52,9 @@ __device__ __forceinline__ void scale_from_minmax(float mn, float mx, float maxv
     scale = (scale_inv == 0.0f) ? 0.0f : __fdiv_rn(1.0f, scale_inv);
 }
 
+// 512 threads per SM (128 registers each): four CTAs at 4 bits, two at 2 bits.
 template <int BITS, int GROUP, bool BF16>
-__global__ void __launch_bounds__(64 * (32 * (16 / BITS) / 64))
+__global__ void __launch_bounds__(64 * (32 * (16 / BITS) / 64), 512 / (64 * (32 * (16 / BITS) / 64)))
 bd_pack_kernel(const PackParams p) {
     constexpr int P = 16 / BITS;            // codes per 16-bit word
     constexpr int NB = 32 * P;              // tokens per pack block
@@ -142,12 +147,18 @@ bd_pack_kernel(const PackParams p) {
 #pragma unroll
         for (int pi = 0; pi < PPT; ++pi) {
             uint32_t lo = 0, hi = 0;
-#pragma unroll
-            for (int j = 0; j < P; ++j) {
-                const float2 x = pair_to_float2<BF16>(raw[pi][j]);
-                const int gk = j / FPG;
-                lo |= quant_code(x.x, mn[gk][0], sinv[gk][0], maxv) << (BITS * j);
-                hi |= quant_code(x.y, mn[gk][1], sinv[gk][1], maxv) << (BITS * j);
+            auto put = [&](auto jc) {
+                constexpr int J = decltype(jc)::value;
+                const float2 x = pair_to_float2<BF16>(raw[pi][J]);
+                constexpr int gk = J / FPG;
+                lo = put_field<BITS, J>(lo, quant_bits(x.x, mn[gk][0], sinv[gk][0]));
+                hi = put_field<BITS, J>(hi, quant_bits(x.y, mn[gk][1], sinv[gk][1]));
+            };
+            put(std::integral_constant<int, 0>{}); put(std::integral_constant<int, 1>{});
+            put(std::integral_constant<int, 2>{}); put(std::integral_constant<int, 3>{});
+            if constexpr (P == 8) {
+                put(std::integral_constant<int, 4>{}); put(std::integral_constant<int, 5>{});
+                put(std::integral_constant<int, 6>{}); put(std::integral_constant<int, 7>{});
             }
             *reinterpret_cast<uint32_t *>(kp + static_cast<int64_t>(pi) * p.h_k * D) = lo | (hi << 16);
         }
@@ -199,12 +210,18 @@ bd_pack_kernel(const PackParams p) {
                     }
                 }
                 uint32_t lo = 0, hi = 0;
-#pragma unroll
-                for (int j = 0; j < P; ++j) {
-                    const float2 x = pair_to_float2<BF16>(raw[u][j]);
-                    const int gd = j / FPGV;
-                    lo |= quant_code(x.x, mn[gd], sinv[gd], maxv) << (BITS * j);
-                    hi |= quant_code(x.y, mn[gd], sinv[gd], maxv) << (BITS * j);
+                auto put = [&](auto jc) {
+                    constexpr int J = decltype(jc)::value;
+                    const float2 x = pair_to_float2<BF16>(raw[u][J]);
+                    constexpr int gd = J / FPGV;
+                    lo = put_field<BITS, J>(lo, quant_bits(x.x, mn[gd], sinv[gd]));
+                    hi = put_field<BITS, J>(hi, quant_bits(x.y, mn[gd], sinv[gd]));
+                };
+                put(std::integral_constant<int, 0>{}); put(std::integral_constant<int, 1>{});
+                put(std::integral_constant<int, 2>{}); put(std::integral_constant<int, 3>{});
+                if constexpr (P == 8) {
+                    put(std::integral_constant<int, 4>{}); put(std::integral_constant<int, 5>{});
+                    put(std::integral_constant<int, 6>{}); put(std::integral_constant<int, 7>{});
                 }
                 *reinterpret_cast<uint32_t *>(vp + static_cast<int64_t>(t) * p.h_k * DP) = lo | (hi << 16);
             }
