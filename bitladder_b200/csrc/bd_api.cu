@@ -273,7 +273,7 @@ int bd_pack(const bd_pack_args *a, bd_stream_t stream) {
     if (a->dtype != BD_FP16 && a->dtype != BD_BF16) return BD_ERR_UNSUPPORTED;
     const int nb = pack_block_tokens(a->bits);
     if (a->s % nb || a->dst_token_offset % nb) return BD_ERR_INVALID;
-    if (a->h_k > 65535 || a->b > 65535) return BD_ERR_INVALID;
+    if (a->s / nb > 65535 || a->b > 65535) return BD_ERR_INVALID;      // grid.y, grid.z
     if ((reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v) |
          reinterpret_cast<uintptr_t>(a->k_pack) | reinterpret_cast<uintptr_t>(a->v_pack) |
          reinterpret_cast<uintptr_t>(a->k_params) | reinterpret_cast<uintptr_t>(a->v_params)) & 3u)

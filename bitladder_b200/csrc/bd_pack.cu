@@ -52,13 +52,17 @@ __device__ __forceinline__ void scale_from_minmax(float mn, float mx, float maxv
     scale = (scale_inv == 0.0f) ? 0.0f : __fdiv_rn(1.0f, scale_inv);
 }
 
-// 512 threads per SM (128 registers each): four CTAs at 4 bits, two at 2 bits.
+// Four token subsets of 64 threads per CTA; resident threads per SM (and with them the
+// registers a thread may hold) chosen by measurement: 768 at 4 bits, 512 at 2 bits, where a
+// thread keeps twice as many fields.
+constexpr int kPackSubsets = 4;
+constexpr int kPackThreads = 64 * kPackSubsets;
 template <int BITS, int GROUP, bool BF16>
-__global__ void __launch_bounds__(64 * (32 * (16 / BITS) / 64), 512 / (64 * (32 * (16 / BITS) / 64)))
+__global__ void __launch_bounds__(kPackThreads, (BITS == 4 ? 768 : 512) / kPackThreads)
 bd_pack_kernel(const PackParams p) {
     constexpr int P = 16 / BITS;            // codes per 16-bit word
     constexpr int NB = 32 * P;              // tokens per pack block
-    constexpr int NT = NB / 64;             // token subsets (threads = 64 * NT)
+    constexpr int NT = kPackSubsets;        // token subsets (threads = 64 * NT)
     constexpr int NTHREADS = 64 * NT;
     constexpr int PPT = 32 / NT;            // pack rows per thread (K)
     constexpr int NGK = NB / GROUP;         // K token groups per block
@@ -77,7 +81,8 @@ bd_pack_kernel(const PackParams p) {
     __shared__ __half vprm[NGD][2][NB];
 
     const int tid = threadIdx.x;
-    const int blk = blockIdx.x, ih = blockIdx.y, ib = blockIdx.z;
+    // heads vary fastest: CTAs that run together read neighbouring 256-byte pieces of the same token rows
+    const int ih = blockIdx.x, blk = blockIdx.y, ib = blockIdx.z;
     const int dst_blk = blk + p.dst_token_offset / NB;
     const uint16_t *kin = static_cast<const uint16_t *>(p.k);
     const uint16_t *vin = static_cast<const uint16_t *>(p.v);
@@ -247,8 +252,8 @@ bd_pack_kernel(const PackParams p) {
 template <int BITS, int GROUP, bool BF16>
 static cudaError_t launch_pack_t(const PackParams &p, cudaStream_t stream) {
     constexpr int NB = 32 * (16 / BITS);
-    constexpr int NTHREADS = 64 * (NB / 64);
-    dim3 grid(p.s / NB, p.h_k, p.b);
+    constexpr int NTHREADS = kPackThreads;
+    dim3 grid(p.h_k, p.s / NB, p.b);
     bd_pack_kernel<BITS, GROUP, BF16><<<grid, NTHREADS, 0, stream>>>(p);
     return cudaGetLastError();
 }
