@@ -265,6 +265,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-preroll", action="store_true", help="skip the half-second clock pre-roll (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--num-splits", type=int, default=0, help="ranges per sequence (0: the library's plan)")
     ap.add_argument("--graph-steps", type=int, default=48, help="decode steps held by one CUDA graph")
     ap.add_argument("--eager", action="store_true", help="launch every step from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
@@ -298,13 +299,14 @@ def main():
     nbytes = algorithmic_bytes(w, seqlens, res_lens)
     out = torch.empty_like(q)
 
-    ws_bytes = B.decode_workspace_bytes(q, *caches[0], group_size=w["group"], num_bits=w["bits"], **extras)
+    ws_bytes = B.decode_workspace_bytes(q, *caches[0], group_size=w["group"], num_bits=w["bits"],
+                                        num_splits=args.num_splits, **extras)
     workspace = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device=device)
 
     def step(i):
         bufs = caches[i % len(caches)]
         B.fwd_kvcache_int(q, bufs[0], bufs[1], bufs[2], bufs[3], None, scale, "k-channel", w["group"], w["bits"],
-                          out=out, workspace=workspace, **extras)
+                          out=out, workspace=workspace, num_splits=args.num_splits, **extras)
 
     def barrier():
         if distributed:

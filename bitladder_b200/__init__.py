@@ -14,3 +14,4 @@ from .bit_decode_interface import (  # noqa: F401
     pack_block_tokens,
     alloc_packed_cache,
 )
+from .kv_cache import PackedKVCache  # noqa: F401

@@ -248,11 +248,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     int *arrivals = reinterpret_cast<int *>(smem + C::OFF_FLAGS + 16);     // per first sharing warp of a segment
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef BD_EXP_ROTHEAD
-    const int ih = blockIdx.x % p.h_k, row = (blockIdx.x / p.h_k + ih * BD_EXP_ROTHEAD) % p.part.R;
-#else
     const int ih = blockIdx.x % p.h_k, row = blockIdx.x / p.h_k;
-#endif
     const int g = lane >> 2, l = lane & 3;
     if ((smem_base & 1023u) != 0) {                      // never seen; refuse rather than read garbage
         if (tid == 0) atomicExch(p.status, BD_ERR_ALIGNMENT);
