@@ -274,12 +274,13 @@ int bd_pack(const bd_pack_args *a, bd_stream_t stream) {
     const int nb = pack_block_tokens(a->bits);
     if (a->s % nb || a->dst_token_offset % nb) return BD_ERR_INVALID;
     if (a->s / nb > 65535 || a->b > 65535) return BD_ERR_INVALID;      // grid.y, grid.z
+    // 16-byte vector loads of the inputs and 16-byte stores of the V codes
     if ((reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v) |
          reinterpret_cast<uintptr_t>(a->k_pack) | reinterpret_cast<uintptr_t>(a->v_pack) |
-         reinterpret_cast<uintptr_t>(a->k_params) | reinterpret_cast<uintptr_t>(a->v_params)) & 3u)
+         reinterpret_cast<uintptr_t>(a->k_params) | reinterpret_cast<uintptr_t>(a->v_params)) & 15u)
         return BD_ERR_ALIGNMENT;
     if ((a->k_stride_b | a->k_stride_s | a->k_stride_h | a->v_stride_b | a->v_stride_s | a->v_stride_h |
-         a->k_pack_stride_b | a->v_pack_stride_b) & 1)
+         a->k_pack_stride_b | a->v_pack_stride_b) & 7)
         return BD_ERR_ALIGNMENT;
     if (a->s == 0) return BD_OK;
     DeviceInfo info;

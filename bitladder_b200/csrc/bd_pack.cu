@@ -71,10 +71,6 @@ bd_pack_kernel(const PackParams p) {
     constexpr int DP = D / P;               // words per V row
     constexpr int NGD = D / GROUP;          // V dim groups
     constexpr int FPGV = P / NGD;           // V fields per dim group
-    constexpr int LPT = DP / 2;             // lanes per token (V)
-    constexpr int TPI = NTHREADS / LPT;     // tokens per iteration (V)
-    constexpr int VITER = NB / TPI;
-    constexpr int VU = (VITER >= 4) ? 4 : VITER;   // V iterations loaded together
     const float maxv = static_cast<float>((1 << BITS) - 1);
 
     __shared__ float red[NT][NGK][2][D];
@@ -171,53 +167,66 @@ bd_pack_kernel(const PackParams p) {
 
     // ------------------------------------------------------------------ V
     {
-        const int li = tid % LPT, tsub = tid / LPT;
+        // A thread owns 8 consecutive output words of one token (one 16-byte store) and so needs,
+        // for every field j, the 8 dims  p0 + DP*j .. +7: P loads of 16 bytes.  DP/8 threads per token
+        // (4 at 4 bits, 2 at 2 bits): the min/max over a token's group takes one or two shuffles.
+        constexpr int TPT = DP / 8;              // threads per token
+        constexpr int TPI = NTHREADS / TPT;      // tokens per iteration
+        constexpr int VITER = NB / TPI;
+        static_assert(VITER * TPI == NB, "token tiling");
+        const int q8 = tid % TPT, tsub = tid / TPT;
         const uint16_t *vbase = vin + ib * p.v_stride_b + static_cast<int64_t>(blk) * NB * p.v_stride_s +
-                                ih * p.v_stride_h + 2 * li;
+                                ih * p.v_stride_h + 8 * q8;
         uint16_t *vp = static_cast<uint16_t *>(p.v_pack) + ib * p.v_pack_stride_b +
-                       (static_cast<int64_t>(dst_blk) * NB * p.h_k + ih) * DP + 2 * li;
-#pragma unroll 1
-        for (int it0 = 0; it0 < VITER; it0 += VU) {
-            uint32_t raw[VU][P];
+                       (static_cast<int64_t>(dst_blk) * NB * p.h_k + ih) * DP + 8 * q8;
+        uint4 raw[VITER][P];
 #pragma unroll
-            for (int u = 0; u < VU; ++u) {
-                const int t = (it0 + u) * TPI + tsub;
+        for (int u = 0; u < VITER; ++u) {
+            const int t = u * TPI + tsub;
 #pragma unroll
-                for (int j = 0; j < P; ++j)
-                    raw[u][j] = __ldg(reinterpret_cast<const unsigned int *>(vbase + t * p.v_stride_s + DP * j));
-            }
+            for (int j = 0; j < P; ++j)
+                raw[u][j] = __ldg(reinterpret_cast<const uint4 *>(vbase + t * p.v_stride_s + DP * j));
+        }
 #pragma unroll
-            for (int u = 0; u < VU; ++u) {
-                const int t = (it0 + u) * TPI + tsub;
-                float mn[NGD], mx[NGD];
+        for (int u = 0; u < VITER; ++u) {
+            const int t = u * TPI + tsub;
+            float mn[NGD], mx[NGD];
 #pragma unroll
-                for (int gd = 0; gd < NGD; ++gd) { mn[gd] = INFINITY; mx[gd] = -INFINITY; }
+            for (int gd = 0; gd < NGD; ++gd) { mn[gd] = INFINITY; mx[gd] = -INFINITY; }
 #pragma unroll
-                for (int j = 0; j < P; ++j) {
-                    const float2 x = pair_to_float2<BF16>(raw[u][j]);
-                    const int gd = j / FPGV;
+            for (int j = 0; j < P; ++j) {
+                const int gd = j / FPGV;
+                const uint32_t w4[4] = {raw[u][j].x, raw[u][j].y, raw[u][j].z, raw[u][j].w};
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const float2 x = pair_to_float2<BF16>(w4[r]);
                     mn[gd] = fminf(mn[gd], fminf(x.x, x.y));
                     mx[gd] = fmaxf(mx[gd], fmaxf(x.x, x.y));
                 }
-                float sinv[NGD];
+            }
+            float sinv[NGD];
 #pragma unroll
-                for (int gd = 0; gd < NGD; ++gd) {
+            for (int gd = 0; gd < NGD; ++gd) {
 #pragma unroll
-                    for (int off = 1; off < LPT; off <<= 1) {
-                        mn[gd] = fminf(mn[gd], __shfl_xor_sync(0xffffffffu, mn[gd], off));
-                        mx[gd] = fmaxf(mx[gd], __shfl_xor_sync(0xffffffffu, mx[gd], off));
-                    }
-                    float sc;
-                    scale_from_minmax(mn[gd], mx[gd], maxv, sinv[gd], sc);
-                    if (li == 0) {
-                        vprm[gd][0][t] = __float2half_rn(sc);
-                        vprm[gd][1][t] = __float2half_rn(mn[gd]);
-                    }
+                for (int off = 1; off < TPT; off <<= 1) {
+                    mn[gd] = fminf(mn[gd], __shfl_xor_sync(0xffffffffu, mn[gd], off));
+                    mx[gd] = fmaxf(mx[gd], __shfl_xor_sync(0xffffffffu, mx[gd], off));
                 }
+                float sc;
+                scale_from_minmax(mn[gd], mx[gd], maxv, sinv[gd], sc);
+                if (q8 == 0) {
+                    vprm[gd][0][t] = __float2half_rn(sc);
+                    vprm[gd][1][t] = __float2half_rn(mn[gd]);
+                }
+            }
+            uint32_t outw[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
                 uint32_t lo = 0, hi = 0;
                 auto put = [&](auto jc) {
                     constexpr int J = decltype(jc)::value;
-                    const float2 x = pair_to_float2<BF16>(raw[u][J]);
+                    const uint32_t w = r == 0 ? raw[u][J].x : (r == 1 ? raw[u][J].y : (r == 2 ? raw[u][J].z : raw[u][J].w));
+                    const float2 x = pair_to_float2<BF16>(w);
                     constexpr int gd = J / FPGV;
                     lo = put_field<BITS, J>(lo, quant_bits(x.x, mn[gd], sinv[gd]));
                     hi = put_field<BITS, J>(hi, quant_bits(x.y, mn[gd], sinv[gd]));
@@ -228,8 +237,9 @@ bd_pack_kernel(const PackParams p) {
                     put(std::integral_constant<int, 4>{}); put(std::integral_constant<int, 5>{});
                     put(std::integral_constant<int, 6>{}); put(std::integral_constant<int, 7>{});
                 }
-                *reinterpret_cast<uint32_t *>(vp + static_cast<int64_t>(t) * p.h_k * DP) = lo | (hi << 16);
+                outw[r] = lo | (hi << 16);
             }
+            *reinterpret_cast<uint4 *>(vp + static_cast<int64_t>(t) * p.h_k * DP) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
         }
         __syncthreads();
         // scales / zeros of this block's tokens: per dim group, per run of 128 tokens,
