@@ -17,7 +17,9 @@ Differences from the reference, all of them additions or stricter checks:
   arguments but has no kernels for them);
 * unsupported ``(quant_mode, group_size, num_bits, dtype)`` combinations raise
   instead of silently doing nothing (reference: ``csrc/bit_decode/decode_api.cpp:207-226``);
-* paged caches (``opt_block_table``) are not implemented and raise.
+* paged caches (``opt_block_table``): the four packed buffers then hold pages of 256-token
+  multiples instead of sequences, as in the reference (``decode_api.cpp:328-352``); the pack
+  call packs every page of the pool it is given.
 """
 from __future__ import annotations
 
@@ -137,7 +139,10 @@ def kvcache_pack_int(k_cache: torch.Tensor, k_pack: torch.Tensor, k_params: torc
     Asynchronous on the current stream.
     """
     _check_config(quant_mode, group_size, num_bits)
-    _require(opt_block_table is None, "paged KV caches (opt_block_table) are not supported")
+    # A paged pool is packed page by page: quantization groups never cross a pack block, so the
+    # pages are just `num_pages` independent sequences of `page_size` tokens and the table is not needed.
+    if opt_block_table is not None:
+        _require(k_cache.dim() == 4 and k_cache.shape[1] % 256 == 0, "Paged KV cache block size must be divisible by 256")
     _check_cuda(k_cache, v_cache, k_pack, k_params, v_pack, v_params)
     _require(k_cache.dtype in (torch.float16, torch.bfloat16), "k_cache must be fp16 or bf16")
     _require(v_cache.dtype == k_cache.dtype, "k_cache and v_cache must have the same dtype")
@@ -169,17 +174,28 @@ def kvcache_pack_int(k_cache: torch.Tensor, k_pack: torch.Tensor, k_params: torc
 
 
 def _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
-                 k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, lse, num_splits):
+                 k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, lse, num_splits, block_table=None):
     b, s_cap, h_k, d = _check_packed(k_pack, k_params, v_pack, v_params, num_bits, group_size)
     _require(q.dim() == 4 and q.shape[1] == 1, "q must be (b, 1, h, d): one query token per sequence")
+    num_pages = 0
+    if block_table is not None:
+        # paged cache (reference: decode_api.cpp:328-352): the buffers hold pages, not sequences
+        _require(block_table.dtype == torch.int32, "block_table must have dtype torch.int32")
+        _require(block_table.dim() == 2 and block_table.stride(-1) == 1,
+                 "block_table must be (b, max_blocks) with a contiguous last dimension")
+        _require(s_cap % 256 == 0, "Paged KV cache block size must be divisible by 256")
+        num_pages, b = b, block_table.shape[0]
     _require(q.shape[0] == b and q.shape[3] == d, "q does not match the packed cache's batch / head_dim")
     h = q.shape[2]
     _require(h % h_k == 0, "Number of heads in key/value must divide number of heads in query")
     _require(h // h_k <= 16, "at most 16 query heads per KV head are supported")
     _require(q.stride(-1) == 1, "Input tensor must have contiguous last dimension")
-    s = s_cap if seqlen_k is None else int(seqlen_k)
-    _require(0 <= s <= s_cap, "seqlen_k exceeds the packed buffers")
+    s_max = s_cap if block_table is None else s_cap * block_table.shape[1]
+    s = s_max if seqlen_k is None else int(seqlen_k)
+    _require(0 <= s <= s_max, "seqlen_k exceeds the packed buffers")
     a = _lib.DecodeArgs()
+    if block_table is not None:
+        a.block_table, a.block_table_stride, a.num_pages = block_table.data_ptr(), block_table.stride(0), num_pages
     a.q, a.out, a.lse = q.data_ptr(), out.data_ptr(), (lse.data_ptr() if lse is not None else None)
     a.q_stride_b, a.q_stride_h = q.stride(0), q.stride(2)
     a.out_stride_b, a.out_stride_h = out.stride(0), out.stride(2)
@@ -272,8 +288,8 @@ def fwd_kvcache_int(q: torch.Tensor,
     with changes).  Asynchronous on the current stream.
     """
     _check_config(quant_mode, group_size, num_bits)
-    _require(opt_block_table is None, "paged KV caches (opt_block_table) are not supported")
-    _check_cuda(q, k_pack, k_params, v_pack, v_params, k_res, v_res, res_lens, cache_seqlens, out, workspace)
+    _check_cuda(q, k_pack, k_params, v_pack, v_params, k_res, v_res, res_lens, cache_seqlens, out, workspace,
+                opt_block_table)
     _require(q.dtype in (torch.float16, torch.bfloat16), "q must be fp16 or bf16")
     if out is None:
         out = torch.empty(q.shape, dtype=out_dtype or q.dtype, device=q.device)
@@ -281,7 +297,7 @@ def fwd_kvcache_int(q: torch.Tensor,
         _require(out.shape == q.shape and out.stride(-1) == 1, "out must have q's shape and a contiguous last dimension")
     lse = torch.empty((q.shape[0], q.shape[2]), dtype=torch.float32, device=q.device) if return_lse else None
     a = _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
-                     k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, lse, num_splits)
+                     k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, lse, num_splits, opt_block_table)
     with torch.cuda.device(q.device):
         ws = _workspace_for(a, q.device, workspace)
         _lib.check(_lib.load().bd_decode(C.byref(a), _stream(q.device)), "bd_decode")
@@ -291,11 +307,11 @@ def fwd_kvcache_int(q: torch.Tensor,
 
 def decode_workspace_bytes(q, k_pack, k_params, v_pack, v_params, group_size=128, num_bits=4,
                            seqlen_k=None, num_splits=0, k_res=None, v_res=None, res_lens=None,
-                           cache_seqlens=None) -> int:
+                           cache_seqlens=None, block_table=None) -> int:
     """Bytes of workspace a decode call with these tensors needs (the tail and
     per-sequence lengths add to it, so pass them if the call will)."""
     a = _decode_args(q, k_pack, k_params, v_pack, v_params, 1.0, group_size, num_bits,
-                     k_res, v_res, res_lens, cache_seqlens, seqlen_k, q, None, num_splits)
+                     k_res, v_res, res_lens, cache_seqlens, seqlen_k, q, None, num_splits, block_table)
     with torch.cuda.device(q.device):
         return int(_lib.load().bd_decode_workspace_bytes(C.byref(a)))
 

@@ -148,7 +148,13 @@ int check_decode_args(const bd_decode_args *a) {
     if (a->h % a->h_k) return BD_ERR_INVALID;
     if (a->h / a->h_k > 16) return BD_ERR_UNSUPPORTED;
     const int nb = pack_block_tokens(a->bits);
-    if (a->s_cap % nb || a->s > a->s_cap) return BD_ERR_INVALID;
+    if (a->block_table == nullptr) {
+        if (a->s_cap % nb || a->s > a->s_cap) return BD_ERR_INVALID;
+    } else {
+        // paged: s_cap is the page size (reference: a multiple of 256, decode_api.cpp:351)
+        if (a->s_cap % 256 || a->num_pages <= 0 || a->block_table_stride <= 0) return BD_ERR_INVALID;
+        if (int64_t(a->s) > int64_t(a->block_table_stride) * a->s_cap) return BD_ERR_INVALID;
+    }
     if ((a->k_res == nullptr) != (a->v_res == nullptr)) return BD_ERR_INVALID;
     if (a->k_res && (a->res_len < 0 || a->res_len > 256)) return BD_ERR_UNSUPPORTED;
     if (!aligned16(a->q) || !aligned16(a->out) || !aligned16(a->k_pack) || !aligned16(a->k_params) ||
@@ -332,8 +338,9 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     const int P = 16 / a->bits, nb = 32 * P, dp = 128 / P;
     const int64_t k_row = int64_t(a->h_k) * 128, v_row = int64_t(a->h_k) * dp;
     const int64_t k_batch_rows = a->k_pack_stride_b / k_row, v_batch_rows = a->v_pack_stride_b / v_row;
-    const uint64_t k_rows_total = uint64_t(a->b - 1) * k_batch_rows + uint64_t(a->s_cap / P);
-    const uint64_t v_rows_total = uint64_t(a->b - 1) * v_batch_rows + uint64_t(a->s_cap);
+    const int64_t units = a->block_table ? a->num_pages : a->b;      // sequences, or pages of a paged cache
+    const uint64_t k_rows_total = uint64_t(units - 1) * k_batch_rows + uint64_t(a->s_cap / P);
+    const uint64_t v_rows_total = uint64_t(units - 1) * v_batch_rows + uint64_t(a->s_cap);
     if (k_rows_total > 0x7fffffffull || v_rows_total > 0x7fffffffull) return BD_ERR_INVALID;
     if (int64_t(plan.rows) * a->h_k > 0x7fffffffll) return BD_ERR_INVALID;
 
@@ -374,6 +381,9 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     p.v_params_stride_g = 2 * a->v_params_stride_g;
     p.v_params_stride_h = 2 * a->v_params_stride_h;
     p.cache_seqlens = a->cache_seqlens;
+    p.block_table = a->block_table;
+    p.block_table_stride = a->block_table_stride;
+    p.blocks_per_page = a->block_table ? a->s_cap / nb : 0;
     p.k_res = a->k_res; p.v_res = a->v_res;
     p.res_stride_b = a->res_stride_b; p.res_stride_s = a->res_stride_s; p.res_stride_h = a->res_stride_h;
     p.res_lens = a->res_lens; p.res_len = a->k_res ? a->res_len : 0;

@@ -279,7 +279,18 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     const int wrow = row * kWarps + warp;
 
     // ---- TMA issue (one lane) ------------------------------------------------
+    // Paged cache: block `blk` of sequence `ib` sits in page block_table[ib][blk / blocks_per_page]
+    // at block blk % blocks_per_page; the page takes the place of the batch index in every address
+    // below (pages are laid out exactly like the sequences of a contiguous cache).
+    auto resolve = [&](int &ib, int &blk) {
+        if (p.block_table != nullptr) {
+            const int pg = blk / p.blocks_per_page;
+            blk -= pg * p.blocks_per_page;
+            ib = p.block_table[int64_t(ib) * p.block_table_stride + pg];
+        }
+    };
     auto issue_k = [&](int ib, int blk) {
+        resolve(ib, blk);
         mbar_arrive_expect_tx(kbar, C::CODE_BYTES + PRM);
         const int row0 = ib * p.k_batch_rows + blk * 32;
         tma_load_2d(kcode, &kmap, kbar, ih * kHeadDim, row0);
@@ -290,6 +301,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             bulk_load_1d(kprm + gk * 512, src + ((int64_t(blk) * NGK + gk) * p.h_k + ih) * (2 * kHeadDim), 512, kbar);
     };
     auto issue_v = [&](int ib, int blk) {
+        resolve(ib, blk);
         mbar_arrive_expect_tx(vbar, C::CODE_BYTES + PRM);
         tma_load_2d(vcode, &vmap, vbar, ih * DP, ib * p.v_batch_rows + blk * NB);
         const uint16_t *src = p.v_params + ib * p.v_params_stride_b + ih * p.v_params_stride_h;

@@ -179,6 +179,8 @@ struct DecodeParams {
     int64_t k_params_stride_b;    // in fp16 elements
     int64_t v_params_stride_b, v_params_stride_g, v_params_stride_h;   // in fp16 elements
     const int32_t *cache_seqlens;
+    const int32_t *block_table;   // paged cache: [b][block_table_stride] page indices; null: contiguous
+    int32_t block_table_stride, blocks_per_page;
     const void *k_res, *v_res;
     int64_t res_stride_b, res_stride_s, res_stride_h;
     const int32_t *res_lens;

@@ -134,6 +134,14 @@ typedef struct bd_decode_args {
     int32_t out_dtype;        /* BD_FP16 / BD_BF16 / BD_FP32 */
     float softmax_scale;
     int32_t num_splits;       /* 0 = choose (bd_plan_splits); n > 0 = about n ranges per sequence */
+    /* Paged cache (reference: block_table, decode_api.cpp:328-352): when block_table is not null
+     * the four packed buffers hold `num_pages` pages of `page_size` tokens each instead of b
+     * sequences of s_cap tokens (same layout, the *_stride_b fields step from page to page,
+     * s_cap must equal page_size), and tokens [i*page_size, (i+1)*page_size) of sequence ib
+     * live in page block_table[ib * block_table_stride + i].  page_size is a multiple of 256. */
+    const int32_t *block_table;
+    int32_t block_table_stride; /* entries per sequence (>= ceil(s / page_size)) */
+    int32_t num_pages;
     void *workspace;
     size_t workspace_bytes;
 } bd_decode_args;

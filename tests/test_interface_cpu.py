@@ -53,11 +53,12 @@ def test_unsupported_configs_raise_instead_of_doing_nothing(kw, msg):
         B.fwd_kvcache_int(q, *bufs, **kw)
 
 
-def test_paged_cache_is_refused():
+def test_paged_cache_checks_its_page_size():
+    """The reference's own check: pages are multiples of 256 tokens (decode_api.cpp:351, 566)."""
     k = torch.zeros(1, 128, 2, 128, dtype=torch.float16)
     bufs = _cpu_buffers()
     table = torch.zeros(1, 1, dtype=torch.int32)
-    with pytest.raises(RuntimeError, match="paged"):
+    with pytest.raises(RuntimeError, match="divisible by 256"):
         B.kvcache_pack_int(k, bufs[0], bufs[1], k, bufs[2], bufs[3], table)
 
 
