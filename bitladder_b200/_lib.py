@@ -56,6 +56,7 @@ class DecodeArgs(C.Structure):
         ("dtype", C.c_int32), ("out_dtype", C.c_int32),
         ("softmax_scale", C.c_float),
         ("num_splits", C.c_int32),
+        ("k_new", C.c_void_p), ("v_new", C.c_void_p), ("new_stride_b", C.c_int64), ("new_stride_h", C.c_int64),
         ("block_table", C.c_void_p), ("block_table_stride", C.c_int32), ("num_pages", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]

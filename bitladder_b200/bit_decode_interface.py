@@ -174,7 +174,8 @@ def kvcache_pack_int(k_cache: torch.Tensor, k_pack: torch.Tensor, k_params: torc
 
 
 def _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
-                 k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, lse, num_splits, block_table=None):
+                 k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, lse, num_splits, block_table=None,
+                 k_new=None, v_new=None):
     b, s_cap, h_k, d = _check_packed(k_pack, k_params, v_pack, v_params, num_bits, group_size)
     _require(q.dim() == 4 and q.shape[1] == 1, "q must be (b, 1, h, d): one query token per sequence")
     num_pages = 0
@@ -224,6 +225,16 @@ def _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_siz
             _require(res_lens.dtype == torch.int32 and res_lens.numel() == b and res_lens.is_contiguous(),
                      "res_lens must be a contiguous int32 tensor of shape (b,)")
             a.res_lens = res_lens.data_ptr()
+    if k_new is not None or v_new is not None:
+        _require(k_new is not None and v_new is not None, "k_new and v_new must be given together")
+        _require(k_res is not None and res_lens is not None,
+                 "k_new/v_new are appended to the tail: k_res, v_res and res_lens are needed")
+        _require(k_new.dtype == q.dtype and v_new.dtype == q.dtype, "k_new/v_new must have q's dtype")
+        _require(tuple(k_new.shape) == (b, 1, h_k, d) and k_new.shape == v_new.shape and k_new.stride() == v_new.stride(),
+                 "k_new and v_new must both be (b, 1, h_k, d) with equal strides")
+        _require(k_new.stride(-1) == 1, "Input tensor must have contiguous last dimension")
+        a.k_new, a.v_new = k_new.data_ptr(), v_new.data_ptr()
+        a.new_stride_b, a.new_stride_h = k_new.stride(0), k_new.stride(2)
     a.b, a.h, a.h_k, a.d = b, h, h_k, d
     a.s, a.s_cap = s, s_cap
     a.bits, a.group = num_bits, group_size
@@ -271,7 +282,8 @@ def fwd_kvcache_int(q: torch.Tensor,
                     res_lens: Optional[torch.Tensor] = None, cache_seqlens: Optional[torch.Tensor] = None,
                     seqlen_k: Optional[int] = None, return_lse: bool = False,
                     out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
-                    workspace: Optional[torch.Tensor] = None, num_splits: int = 0):
+                    workspace: Optional[torch.Tensor] = None, num_splits: int = 0,
+                    k_new: Optional[torch.Tensor] = None, v_new: Optional[torch.Tensor] = None):
     """One decode-attention step over the packed cache; returns ``out`` (b, 1, h, d).
 
     Same positional signature as the reference (``bit_decode_interface.py:43-86``),
@@ -285,11 +297,14 @@ def fwd_kvcache_int(q: torch.Tensor,
     ``out_dtype`` (fp16, bf16 or fp32) / ``workspace`` / ``num_splits`` for callers
     that manage memory and scheduling themselves (a caller-provided ``workspace`` must
     be zero-filled once, and again whenever the batch size or KV head count it is used
-    with changes).  Asynchronous on the current stream.
+    with changes); ``k_new``/``v_new`` (b, 1, h_k, d): the K/V rows of the token decoded in this
+    step — the step attends over them as the next tail row and stores them at row ``res_lens[b]`` of
+    ``k_res``/``v_res`` (fused append; the caller then adds one to ``res_lens``, which must be below
+    the tail buffers' length).  Asynchronous on the current stream.
     """
     _check_config(quant_mode, group_size, num_bits)
     _check_cuda(q, k_pack, k_params, v_pack, v_params, k_res, v_res, res_lens, cache_seqlens, out, workspace,
-                opt_block_table)
+                opt_block_table, k_new, v_new)
     _require(q.dtype in (torch.float16, torch.bfloat16), "q must be fp16 or bf16")
     if out is None:
         out = torch.empty(q.shape, dtype=out_dtype or q.dtype, device=q.device)
@@ -297,7 +312,8 @@ def fwd_kvcache_int(q: torch.Tensor,
         _require(out.shape == q.shape and out.stride(-1) == 1, "out must have q's shape and a contiguous last dimension")
     lse = torch.empty((q.shape[0], q.shape[2]), dtype=torch.float32, device=q.device) if return_lse else None
     a = _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
-                     k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, lse, num_splits, opt_block_table)
+                     k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, lse, num_splits, opt_block_table,
+                     k_new, v_new)
     with torch.cuda.device(q.device):
         ws = _workspace_for(a, q.device, workspace)
         _lib.check(_lib.load().bd_decode(C.byref(a), _stream(q.device)), "bd_decode")

@@ -124,7 +124,7 @@ int make_plan(const bd_decode_args *a, int sm_count, DecodePlan &plan) {
     plan.rows = int(std::max<int64_t>(1, std::min<int64_t>(rows, 1 << 20)));
     const bool has_tail = a->k_res != nullptr;
     plan.ragged = a->cache_seqlens != nullptr || (has_tail && a->res_lens != nullptr);
-    plan.n_uniform = bd::seq_blocks(a->s, a->s, nb) + (has_tail ? bd::tail_chunks(a->res_len) : 0);
+    plan.n_uniform = bd::seq_blocks(a->s, a->s, nb) + (has_tail ? bd::tail_chunks(a->res_len + (a->k_new ? 1 : 0)) : 0);
     const size_t slots = (size_t(plan.rows) + a->b) * a->h_k;
     size_t off = 16;                                  // status word
     plan.off_counters = off;
@@ -156,6 +156,10 @@ int check_decode_args(const bd_decode_args *a) {
         if (int64_t(a->s) > int64_t(a->block_table_stride) * a->s_cap) return BD_ERR_INVALID;
     }
     if ((a->k_res == nullptr) != (a->v_res == nullptr)) return BD_ERR_INVALID;
+    if ((a->k_new == nullptr) != (a->v_new == nullptr)) return BD_ERR_INVALID;
+    if (a->k_new && (!a->k_res || !a->res_lens)) return BD_ERR_INVALID;       // appends go to a tail with per-sequence lengths
+    if (a->k_new && (!aligned16(a->k_new) || !aligned16(a->v_new) || a->new_stride_b % 8 || a->new_stride_h % 8))
+        return BD_ERR_ALIGNMENT;
     if (a->k_res && (a->res_len < 0 || a->res_len > 256)) return BD_ERR_UNSUPPORTED;
     if (!aligned16(a->q) || !aligned16(a->out) || !aligned16(a->k_pack) || !aligned16(a->k_params) ||
         !aligned16(a->v_pack) || !aligned16(a->v_params))
@@ -364,6 +368,7 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
         pp.cache_seqlens = a->cache_seqlens;
         pp.res_lens = a->k_res ? a->res_lens : nullptr;
         pp.res_len = a->k_res ? a->res_len : 0;
+        pp.res_extra = a->k_new ? 1 : 0;
         pp.table = reinterpret_cast<int32_t *>(ws + plan.off_table);
         pp.b = a->b; pp.s = a->s; pp.block_tokens = nb;
         err = bd::launch_prefix(pp, stream);
@@ -387,6 +392,10 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     p.k_res = a->k_res; p.v_res = a->v_res;
     p.res_stride_b = a->res_stride_b; p.res_stride_s = a->res_stride_s; p.res_stride_h = a->res_stride_h;
     p.res_lens = a->res_lens; p.res_len = a->k_res ? a->res_len : 0;
+    p.res_cap = p.res_len;
+    p.k_res_out = const_cast<void *>(a->k_res); p.v_res_out = const_cast<void *>(a->v_res);
+    p.k_new = a->k_new; p.v_new = a->v_new;
+    p.new_stride_b = a->new_stride_b; p.new_stride_h = a->new_stride_h;
     p.b = a->b; p.h = a->h; p.h_k = a->h_k; p.gq = a->h / a->h_k;
     p.s = a->s;
     p.k_batch_rows = int32_t(k_batch_rows);

@@ -369,10 +369,26 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
         if (p.cache_seqlens) seqlen = min(max(p.cache_seqlens[ib], 0), p.s);
         int res_n = 0;                                // tail tokens of this sequence
         if (p.k_res != nullptr) res_n = min(max(p.res_lens ? p.res_lens[ib] : p.res_len, 0), kTailMax);
+        // Fused append: the token of this step is tail row res_old.  It is read from k_new / v_new
+        // (nobody reads that row of the tail buffers during this launch) and the warp that streams
+        // it also stores it there, for the steps to come.
+        const int res_old = res_n;
+        const bool has_new = p.k_new != nullptr && res_n < kTailMax;
+        if (has_new) res_n += 1;
         // this warp's units of the sequence: pack blocks [blk0, blk1), tail tokens [tail0, tail1)
         const int nblk = (seqlen + NB - 1) / NB;
         const int blk0 = sg.u0, blk1 = min(sg.u1, nblk);
         const int tail0 = max(sg.u0 - nblk, 0) * kTailChunk, tail1 = min(max(sg.u1 - nblk, 0) * kTailChunk, res_n);
+        if (has_new && res_old >= tail0 && res_old < tail1 && res_old < p.res_cap) {
+            // this warp streams the chunk that holds the new row: it also files the row in the tail
+            // buffers (8 bytes of K and of V per lane), as it came
+            const int64_t src = ib * p.new_stride_b + ih * p.new_stride_h + 4 * lane;
+            const int64_t dst = ib * p.res_stride_b + ih * p.res_stride_h + int64_t(res_old) * p.res_stride_s + 4 * lane;
+            const uint2 kw = __ldg(reinterpret_cast<const uint2 *>(static_cast<const uint16_t *>(p.k_new) + src));
+            const uint2 vw = __ldg(reinterpret_cast<const uint2 *>(static_cast<const uint16_t *>(p.v_new) + src));
+            *reinterpret_cast<uint2 *>(static_cast<uint16_t *>(p.k_res_out) + dst) = kw;
+            *reinterpret_cast<uint2 *>(static_cast<uint16_t *>(p.v_res_out) + dst) = vw;
+        }
 
         // Query rows as B fragments: thread (g, l) holds q[row g][32a + 8l .. +7], a = 0..3.
         uint32_t qr[NQT][4][4];
@@ -426,6 +442,12 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             const uint16_t *vres = static_cast<const uint16_t *>(p.v_res) + ib * p.res_stride_b + ih * p.res_stride_h;
             const uint16_t *kA = kres + int64_t(rA) * p.res_stride_s + 8 * l, *kB = kres + int64_t(rB) * p.res_stride_s + 8 * l;
             const uint16_t *vA = vres + int64_t(rA) * p.res_stride_s + 2 * l, *vB = vres + int64_t(rB) * p.res_stride_s + 2 * l;
+            if (has_new) {
+                const uint16_t *knew = static_cast<const uint16_t *>(p.k_new) + ib * p.new_stride_b + ih * p.new_stride_h;
+                const uint16_t *vnew = static_cast<const uint16_t *>(p.v_new) + ib * p.new_stride_b + ih * p.new_stride_h;
+                if (rA == res_old) { kA = knew + 8 * l; vA = vnew + 2 * l; }
+                if (rB == res_old) { kB = knew + 8 * l; vB = vnew + 2 * l; }
+            }
             uint4 ka[4], kb[4];
 #pragma unroll
             for (int a = 0; a < 4; ++a) {
@@ -1128,7 +1150,7 @@ __global__ void __launch_bounds__(256) bd_prefix_kernel(const PrefixParams p) {
     int32_t sum = 0;
     auto units = [&](int i) {
         return seq_blocks(p.cache_seqlens ? p.cache_seqlens[i] : p.s, p.s, p.block_tokens) +
-               tail_chunks(p.res_lens ? p.res_lens[i] : p.res_len);
+               tail_chunks((p.res_lens ? p.res_lens[i] : p.res_len) + p.res_extra);
     };
     for (int i = lo; i < hi; ++i) sum += units(i);
     partial[tid] = sum;

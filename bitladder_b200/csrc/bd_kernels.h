@@ -182,9 +182,13 @@ struct DecodeParams {
     const int32_t *block_table;   // paged cache: [b][block_table_stride] page indices; null: contiguous
     int32_t block_table_stride, blocks_per_page;
     const void *k_res, *v_res;
+    void *k_res_out, *v_res_out;  // the same buffers, written by the fused append
+    const void *k_new, *v_new;    // (b, 1, h_k, d): this step's token, appended to the tail; null: no append
+    int64_t new_stride_b, new_stride_h;
     int64_t res_stride_b, res_stride_s, res_stride_h;
     const int32_t *res_lens;
     int32_t res_len;
+    int32_t res_cap;              // token rows the tail buffers hold
     int32_t b, h, h_k, gq;
     int32_t s;
     int32_t k_batch_rows;         // K batch stride in pack rows
@@ -208,6 +212,7 @@ struct PrefixParams {
     const int32_t *res_lens;          // null: every sequence has res_len tail tokens
     int32_t *table;
     int32_t b, s, block_tokens, res_len;
+    int32_t res_extra;                // 1 when the step appends a token to every tail
 };
 
 struct CombinePartsParams {

@@ -95,28 +95,34 @@ class PackedKVCache:
             self._packed[ib], self._tail[ib] = full, rest
         self._push_lengths()
 
-    def append(self, k_new: torch.Tensor, v_new: torch.Tensor) -> None:
-        """Add one token per sequence, ``(batch, 1, nheads_k, head_dim)``.  A tail that is full is
-        packed first (one ``kvcache_pack_int`` call per sequence that rolls over, usually all at
-        once or none)."""
-        if k_new.shape != (self.batch, 1, self.nheads_k, self.head_dim) or v_new.shape != k_new.shape:
-            raise RuntimeError("append expects (batch, 1, nheads_k, head_dim)")
+    def _roll_full_tails(self) -> None:
+        """Pack every tail that is full as its sequence's next block (one ``kvcache_pack_int`` call per
+        sequence that rolls over, one for the whole batch when all do at the same length)."""
         nb = self.block
         full = [ib for ib in range(self.batch) if self._tail[ib] == nb]
-        if full:
-            if any(self._packed[ib] + nb > self.capacity for ib in full):
-                raise RuntimeError("cache capacity exceeded")
-            same = len(full) == self.batch and len({self._packed[ib] for ib in full}) == 1
-            groups = [list(range(self.batch))] if same else [[ib] for ib in full]
-            for grp in groups:
-                lo, hi = grp[0], grp[-1] + 1
-                kvcache_pack_int(self.k_tail[lo:hi], self.k_pack[lo:hi], self.k_params[lo:hi],
-                                 self.v_tail[lo:hi], self.v_pack[lo:hi], self.v_params[lo:hi],
-                                 None, None, nb, "k-channel", self.group_size, self.num_bits,
-                                 dst_token_offset=self._packed[lo])
-            for ib in full:
-                self._packed[ib] += nb
-                self._tail[ib] = 0
+        if not full:
+            return
+        if any(self._packed[ib] + nb > self.capacity for ib in full):
+            raise RuntimeError("cache capacity exceeded")
+        same = len(full) == self.batch and len({self._packed[ib] for ib in full}) == 1
+        groups = [list(range(self.batch))] if same else [[ib] for ib in full]
+        for grp in groups:
+            lo, hi = grp[0], grp[-1] + 1
+            kvcache_pack_int(self.k_tail[lo:hi], self.k_pack[lo:hi], self.k_params[lo:hi],
+                             self.v_tail[lo:hi], self.v_pack[lo:hi], self.v_params[lo:hi],
+                             None, None, nb, "k-channel", self.group_size, self.num_bits,
+                             dst_token_offset=self._packed[lo])
+        for ib in full:
+            self._packed[ib] += nb
+            self._tail[ib] = 0
+        self._push_lengths()
+
+    def append(self, k_new: torch.Tensor, v_new: torch.Tensor) -> None:
+        """Add one token per sequence, ``(batch, 1, nheads_k, head_dim)``.  A tail that is full is
+        packed first."""
+        if k_new.shape != (self.batch, 1, self.nheads_k, self.head_dim) or v_new.shape != k_new.shape:
+            raise RuntimeError("append expects (batch, 1, nheads_k, head_dim)")
+        self._roll_full_tails()
         if len(set(self._tail)) == 1:                 # every sequence writes the same tail slot
             t = self._tail[0]
             self.k_tail[:, t:t + 1].copy_(k_new)
@@ -140,3 +146,21 @@ class PackedKVCache:
                                k_res=self.k_tail[:, :tail_hi], v_res=self.v_tail[:, :tail_hi],
                                res_lens=self.res_lens, cache_seqlens=self.cache_seqlens,
                                seqlen_k=max(seq_hi, self.block), **kw)
+
+    def append_and_decode(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, softmax_scale: float,
+                          **kw) -> torch.Tensor:
+        """The decoder's step in one launch: attend over everything held plus this step's token
+        ``k_new``/``v_new (batch, 1, nheads_k, head_dim)``, and leave the token in the tail."""
+        if k_new.shape != (self.batch, 1, self.nheads_k, self.head_dim) or v_new.shape != k_new.shape:
+            raise RuntimeError("append_and_decode expects k_new/v_new of shape (batch, 1, nheads_k, head_dim)")
+        self._roll_full_tails()
+        seq_hi = max(self._packed) if self._packed else 0
+        out = fwd_kvcache_int(q, self.k_pack, self.k_params, self.v_pack, self.v_params, None, softmax_scale,
+                              "k-channel", self.group_size, self.num_bits,
+                              k_res=self.k_tail, v_res=self.v_tail, res_lens=self.res_lens,
+                              cache_seqlens=self.cache_seqlens, seqlen_k=max(seq_hi, self.block),
+                              k_new=k_new, v_new=v_new, **kw)
+        for ib in range(self.batch):
+            self._tail[ib] += 1
+        self.res_lens.add_(1)                          # after the step, in stream order
+        return out

@@ -139,6 +139,13 @@ typedef struct bd_decode_args {
      * sequences of s_cap tokens (same layout, the *_stride_b fields step from page to page,
      * s_cap must equal page_size), and tokens [i*page_size, (i+1)*page_size) of sequence ib
      * live in page block_table[ib * block_table_stride + i].  page_size is a multiple of 256. */
+    /* Fused append (no counterpart in the reference snapshot; the scheme of its imgs/scheme.png):
+     * k_new / v_new (b, 1, h_k, d) hold the K/V rows of the token decoded in this step.  The step
+     * attends over them as tail row res_lens[ib] and stores them at that row of k_res / v_res, so
+     * the caller only has to add one to its res_lens afterwards.  Needs res_lens and room in the
+     * tail (res_lens[ib] < res_len, the rows of the tail buffers). */
+    const void *k_new, *v_new;
+    int64_t new_stride_b, new_stride_h;
     const int32_t *block_table;
     int32_t block_table_stride; /* entries per sequence (>= ceil(s / page_size)) */
     int32_t num_pages;

@@ -29,9 +29,12 @@ def _oracle_step(hist_k, hist_v, q, packed_lens, tail_lens, bits, group, dtype):
     return out
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("bits,group,dtype,prompt", [(4, 128, "fp16", [200, 130]), (2, 128, "bf16", [300, 512]),
                                                       (4, 64, "fp16", [0, 127])])
-def test_cache_grows_across_block_boundaries(bits, group, dtype, prompt):
+def test_cache_grows_across_block_boundaries(bits, group, dtype, prompt, fused):
+    """fused=False: append (copies) then decode; fused=True: one launch per step that attends over the
+    new token and stores it in the tail (`append_and_decode`)."""
     from bitladder_b200.kv_cache import PackedKVCache
 
     b, h, h_k, steps = 2, 8, 2, 140
@@ -55,21 +58,30 @@ def test_cache_grows_across_block_boundaries(bits, group, dtype, prompt):
     for step in range(steps):
         k_new = torch.randn(b, 1, h_k, 128, generator=g).to(tdt)
         v_new = torch.randn(b, 1, h_k, 128, generator=g).to(tdt)
-        cache.append(k_new.cuda(), v_new.cuda())
+        q = torch.randn(b, 1, h, 128, generator=g).to(tdt)
+        if fused:
+            out = cache.append_and_decode(q.cuda(), k_new.cuda(), v_new.cuda(), 1.0 / math.sqrt(128))
+        else:
+            cache.append(k_new.cuda(), v_new.cuda())
         for ib in range(b):
             hist_k[ib, lens[ib]] = k_new[ib, 0]
             hist_v[ib, lens[ib]] = v_new[ib, 0]
             lens[ib] += 1
         assert cache.seqlens() == lens
         if step in check_at:
-            q = torch.randn(b, 1, h, 128, generator=g).to(tdt)
-            out = cache.decode(q.cuda(), 1.0 / math.sqrt(128))
+            if not fused:
+                out = cache.decode(q.cuda(), 1.0 / math.sqrt(128))
             packed = list(cache._packed)          # a full tail is packed lazily, at the next append
             tails = [n - p for n, p in zip(lens, packed)]
             assert all(0 < t <= nb for t in tails)
             ref = _oracle_step(hist_k, hist_v, q, packed, tails, bits, group, dtype)
             err = np.abs(out.float().cpu().numpy()[:, 0] - ref).max()
             assert err <= tol, (step, err)
+    # the tails hold exactly the tokens that were appended since the last roll-over
+    for ib in range(b):
+        p_, t_ = cache._packed[ib], cache._tail[ib]
+        assert torch.equal(cache.k_tail[ib, :t_].cpu(), hist_k[ib, p_:p_ + t_])
+        assert torch.equal(cache.v_tail[ib, :t_].cpu(), hist_v[ib, p_:p_ + t_])
 
 
 def test_cache_rejects_bad_calls():
