@@ -6,16 +6,20 @@
 // csrc/bit_decode/src/include/dequantize.h:253-384 and the online softmax of
 // csrc/bit_decode/src/include/softmax.h:188-309); how it computes it does not:
 //
-//  * Work is cut into equal ranges of pack blocks per KV head (see Partition in
-//    bd_kernels.h), one CTA per (range, head), every CTA resident at once.
-//  * A CTA is four independent warps.  Each warp owns whole pack blocks (NB
+//  * Work is cut into equal ranges of units (pack blocks, then chunks of the unquantized
+//    tail) per KV head (see Partition in bd_kernels.h), one CTA per (range, head), one CTA
+//    per SM, every CTA resident at once; inside the CTA the same cut gives every warp one
+//    contiguous range.
+//  * A CTA is up to twelve independent warps.  Each warp owns whole pack blocks (NB
 //    tokens), two shared-memory slots (one K tile, one V tile) and their
 //    mbarriers, and refills a slot itself, with TMA, as soon as it has consumed
 //    it: the next block's K streams in during the V phase and vice versa.  No
-//    warp ever waits for another inside the stream; each keeps its own running
-//    (max, sum, O) and the four are merged once per segment, in registers,
-//    through a 4 KB hand-over buffer.  The unquantized fp16/bf16 tail of a
-//    sequence goes through the same tensor-core path and the same running state.
+//    warp ever waits for another, anywhere in the kernel; each keeps its own running
+//    (max, sum, O).  At the end of a sequence's share the warps that hold a part of it
+//    deposit their partials and count in; the last to count in merges them in a fixed
+//    order, and the CTA that finishes a sequence last merges the CTAs' parts the same
+//    way.  The unquantized fp16/bf16 tail goes through the same tensor-core path and
+//    the same running state.
 //  * Packed codes go global -> shared with tiled TMA copies (128-byte swizzle
 //    for K, 64/32-byte swizzle for V, which makes the transposing ldmatrix on V
 //    bank-conflict free), completion on mbarriers.
@@ -24,7 +28,7 @@
 //    turns into A-fragment registers with one AND per field: the masked field
 //    is read as an fp16 subnormal (code * 2^-24 * 16^k), which the tensor core
 //    multiplies exactly; the power-of-two factor is folded into the softmax
-//    scale (K) or the epilogue (V).
+//    scale (K) or the epilogue (V).  4-bit words come apart in byte pairs (see field()).
 //  * The affine part of the dequantisation is folded out of the inner loop:
 //    per-channel K scales multiply q once per token group, K zeros contribute
 //    q.zero per group (one extra row of MMAs), per-token V scales multiply the
@@ -75,7 +79,11 @@ struct Cfg {
     static constexpr int WARP_BYTES = 2 * CODE_BYTES + 2 * PRM_BYTES + 16;
     static constexpr int FIT = (kSmemLimit - 32) / (WARP_BYTES + 4);
     // two query tiles need more than 168 registers per thread: eight warps leave 255
-    static constexpr int CAP = NQT == 1 ? kMaxWarps : (kMaxWarps < 8 ? kMaxWarps : 8);
+#ifndef BD_MAX_WARPS_2BIT
+#define BD_MAX_WARPS_2BIT 12
+#endif
+    static constexpr int CAP1 = BITS == 2 ? (BD_MAX_WARPS_2BIT < kMaxWarps ? BD_MAX_WARPS_2BIT : kMaxWarps) : kMaxWarps;
+    static constexpr int CAP = NQT == 1 ? CAP1 : (kMaxWarps < 8 ? kMaxWarps : 8);
     static constexpr int WARPS = FIT < CAP ? FIT : CAP;
     static constexpr int THREADS = WARPS * 32;
     static constexpr size_t OFF_PRM = size_t(WARPS) * 2 * CODE_BYTES;
