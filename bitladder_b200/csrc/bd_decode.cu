@@ -78,12 +78,9 @@ struct Cfg {
     // per warp: one K tile and one V tile, then their scales/zeros
     static constexpr int WARP_BYTES = 2 * CODE_BYTES + 2 * PRM_BYTES + 16;
     static constexpr int FIT = (kSmemLimit - 32) / (WARP_BYTES + 4);
-    // two query tiles need more than 168 registers per thread: eight warps leave 255
-#ifndef BD_MAX_WARPS_2BIT
-#define BD_MAX_WARPS_2BIT 12
-#endif
-    static constexpr int CAP1 = BITS == 2 ? (BD_MAX_WARPS_2BIT < kMaxWarps ? BD_MAX_WARPS_2BIT : kMaxWarps) : kMaxWarps;
-    static constexpr int CAP = NQT == 1 ? CAP1 : (kMaxWarps < 8 ? kMaxWarps : 8);
+    // eight fields per word (2 bits) and two query tiles both need more than the 168 registers
+    // twelve warps leave a thread: eight warps (255 registers) measured 3-4 % faster at 2 bits
+    static constexpr int CAP = (NQT == 1 && BITS == 4) ? kMaxWarps : (kMaxWarps < 8 ? kMaxWarps : 8);
     static constexpr int WARPS = FIT < CAP ? FIT : CAP;
     static constexpr int THREADS = WARPS * 32;
     static constexpr size_t OFF_PRM = size_t(WARPS) * 2 * CODE_BYTES;
