@@ -13,5 +13,6 @@ from .bit_decode_interface import (  # noqa: F401
     plan_splits,
     pack_block_tokens,
     alloc_packed_cache,
+    DecodeStep,
 )
 from .kv_cache import PackedKVCache  # noqa: F401

@@ -31,7 +31,7 @@ import torch
 from . import _lib
 
 __all__ = ["kvcache_pack_int", "fwd_kvcache_int", "combine_partials", "decode_workspace_bytes",
-           "plan_splits", "pack_block_tokens", "alloc_packed_cache"]
+           "plan_splits", "pack_block_tokens", "alloc_packed_cache", "DecodeStep"]
 
 _WORKSPACES = {}
 
@@ -319,6 +319,62 @@ def fwd_kvcache_int(q: torch.Tensor,
         _lib.check(_lib.load().bd_decode(C.byref(a), _stream(q.device)), "bd_decode")
     del ws
     return (out, lse) if return_lse else out
+
+
+class DecodeStep:
+    """One decode-attention step, checked and laid out once, launched many times.
+
+    ``fwd_kvcache_int`` validates its tensors and fills the C argument block on every call,
+    some tens of microseconds of Python around a kernel of about sixty.  A decoder loop calls
+    with the same buffers every step (the query buffer, the cache, the tail, the length
+    tensors all stay where they are and only their contents change), so this class does that
+    work once: it takes the same arguments as ``fwd_kvcache_int``, keeps the tensors alive,
+    owns its output (and LSE) buffer and a private zeroed workspace, and ``step()`` is one
+    call into the library on the current stream.  Contents may change between steps
+    (``q.copy_(...)``, ``res_lens += 1``, new rows in the tail); addresses, shapes and strides
+    may not — build a new object when they do.
+    """
+
+    def __init__(self, q, k_pack, k_params, v_pack, v_params, opt_block_table=None, softmax_scale=1.0,
+                 quant_mode="k-channel", group_size=128, num_bits=4, *, k_res=None, v_res=None, res_lens=None,
+                 cache_seqlens=None, seqlen_k=None, return_lse=False, out=None, out_dtype=None, num_splits=0,
+                 k_new=None, v_new=None):
+        _check_config(quant_mode, group_size, num_bits)
+        _check_cuda(q, k_pack, k_params, v_pack, v_params, k_res, v_res, res_lens, cache_seqlens, out,
+                    opt_block_table, k_new, v_new)
+        _require(q.dtype in (torch.float16, torch.bfloat16), "q must be fp16 or bf16")
+        if out is None:
+            out = torch.empty(q.shape, dtype=out_dtype or q.dtype, device=q.device)
+        else:
+            _require(out.shape == q.shape and out.stride(-1) == 1,
+                     "out must have q's shape and a contiguous last dimension")
+        self.out = out
+        self.lse = torch.empty((q.shape[0], q.shape[2]), dtype=torch.float32, device=q.device) if return_lse else None
+        self._args = _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
+                                  k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, self.lse, num_splits,
+                                  opt_block_table, k_new, v_new)
+        self._device = q.device
+        with torch.cuda.device(q.device):
+            need = int(_lib.load().bd_decode_workspace_bytes(C.byref(self._args)))
+            _require(need > 0, "bd_decode_workspace_bytes rejected the arguments")
+            self._workspace = torch.zeros(need, dtype=torch.uint8, device=q.device)
+        self._args.workspace, self._args.workspace_bytes = self._workspace.data_ptr(), need
+        self._keep = (q, k_pack, k_params, v_pack, v_params, opt_block_table, k_res, v_res, res_lens, cache_seqlens,
+                      k_new, v_new)
+        self._fn = _lib.load().bd_decode
+        self._ref = C.byref(self._args)
+
+    def step(self):
+        """Launch the step on the current stream of the tensors' device; returns ``out`` (or
+        ``(out, lse)``), the same buffers every time."""
+        if torch.cuda.current_device() != self._device.index:
+            with torch.cuda.device(self._device):
+                rc = self._fn(self._ref, _stream(self._device))
+        else:
+            rc = self._fn(self._ref, _stream(self._device))
+        if rc != 0:
+            _lib.check(rc, "bd_decode")
+        return (self.out, self.lse) if self.lse is not None else self.out
 
 
 def decode_workspace_bytes(q, k_pack, k_params, v_pack, v_params, group_size=128, num_bits=4,
