@@ -443,6 +443,7 @@ def main():
     traffic_src = ("ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch of this workload"
                    if args.workload == "C2" else "scaled from the C2 capture by algorithmic bytes")
     splits = B.plan_splits(w["b"], w["h_k"], w["s"], w["bits"], torch.cuda.get_device_properties(device).multi_processor_count)
+    rows_used = args.num_splits * w["b"] if args.num_splits > 0 else splits
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -466,7 +467,9 @@ def main():
                          "algorithmic_bytes_per_step": nbytes},
             "cpu_baseline": cpu,
             "e2e": e2e,
-            "gpu_launches": (2 if w["ragged"] else 1) * steps,
+            # decode kernel, + the 256-thread prefix kernel for ragged batches, + the parallel merge
+            # kernel when a sequence is cut into more than four parts on average
+            "gpu_launches": (1 + (1 if w["ragged"] else 0) + (1 if rows_used > 4 * w["b"] else 0)) * steps,
             "clocks": clocks,
             "pack_gb_s": pack_gbs,
         }

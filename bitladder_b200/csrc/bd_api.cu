@@ -413,8 +413,16 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     p.part_out = reinterpret_cast<float *>(ws + plan.off_part_out);
     p.part_lse = reinterpret_cast<float *>(ws + plan.off_part_lse);
 
+    // More than four parts per sequence on average (few long sequences cut over all SMs): one warp
+    // merging them at the end of the decode kernel would be the tail of the step; a second kernel
+    // with a warp per (sequence, query head) does it in parallel.
+    p.defer_merge = plan.rows > 4 * a->b ? 1 : 0;
     err = bd::launch_decode(p, kmap, vmap, a->bits, a->group, stream);
     if (err != cudaSuccess) return BD_ERR_CUDA;
+    if (p.defer_merge) {
+        err = bd::launch_merge_parts(p, stream);
+        if (err != cudaSuccess) return BD_ERR_CUDA;
+    }
 
     return BD_OK;
 }

@@ -976,7 +976,9 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                 else
                     store_rows(static_cast<float *>(p.out) + o0, p.out_stride_h, [](float x) { return x; });
             }
-            if (!final_here) {
+            // With many parts per sequence (few long sequences) the merge is left to a second,
+            // fully parallel kernel: one warp doing it here would be the tail of the whole step.
+            if (!final_here && !p.defer_merge) {
                 // publish the partial, count arrivals; the last one merges (same arithmetic as
                 // the reference's combine kernel, flash_fwd_kernel.h:1217-1231, 1280-1298)
                 __threadfence();
@@ -1141,6 +1143,91 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
         __syncthreads();
         return;
     }
+}
+
+// ---------------------------------------------------------------------------
+// Merge of the CTAs' parts as a kernel of its own, for steps with many parts per sequence
+// (DecodeParams::defer_merge): one warp per (sequence, query head), lane i weighs part i, each
+// lane owns 4 head dims.  Same arithmetic as the in-kernel merge and as the reference's combine
+// (flash_fwd_kernel.h:1217-1231, 1280-1298).  Sequences with at most one part were finished by
+// the decode kernel itself.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) bd_merge_parts_kernel(const DecodeParams p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t rowid = int64_t(blockIdx.x) * 4 + warp;
+    if (rowid >= int64_t(p.b) * p.h) return;
+    const int ib = int(rowid / p.h), hq = int(rowid % p.h);
+    const int ih = hq / p.gq, qrow = hq % p.gq;
+    const PartRange pr = part_range(p.part, ib);
+    const int nrows = pr.c1 - pr.c0 + 1;
+    if (nrows <= 1) return;
+    if (!pr.dense) {
+        int nparts = 0;
+        for (int c = pr.c0; c <= pr.c1; ++c) nparts += row_has_part(p.part, ib, c) ? 1 : 0;
+        if (nparts <= 1) return;
+    }
+    const int64_t slot0 = (int64_t(pr.c0) + ib) * p.h_k + ih;
+    auto lse_of = [&](int i) {
+        const bool live = i < nrows && (pr.dense || row_has_part(p.part, ib, pr.c0 + i));
+        return live ? __ldcg(p.part_lse + (slot0 + int64_t(i) * p.h_k) * p.gq + qrow) : -INFINITY;
+    };
+    float mx = -INFINITY;
+    for (int base = 0; base < nrows; base += 32) mx = fmaxf(mx, lse_of(base + lane));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    float sum = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int base = 0; base < nrows; base += 32) {
+        const float ls = lse_of(base + lane);
+        const float w = (ls == -INFINITY || mx == -INFINITY) ? 0.f : __expf(ls - mx);
+        float t = w;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+        sum += t;
+        const int cnt = min(32, nrows - base);
+        for (int j0 = 0; j0 < cnt; j0 += 8) {
+            float4 v[8];
+            float wj[8];
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+                wj[jj] = __shfl_sync(0xffffffffu, w, (j0 + jj) & 31);
+                if (j0 + jj >= cnt) wj[jj] = 0.f;
+                v[jj] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (wj[jj] != 0.f)
+                    v[jj] = __ldcg(reinterpret_cast<const float4 *>(
+                        p.part_out + ((slot0 + int64_t(base + j0 + jj) * p.h_k) * p.gq + qrow) * kHeadDim + 4 * lane));
+            }
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+                o[0] = fmaf(wj[jj], v[jj].x, o[0]); o[1] = fmaf(wj[jj], v[jj].y, o[1]);
+                o[2] = fmaf(wj[jj], v[jj].z, o[2]); o[3] = fmaf(wj[jj], v[jj].w, o[3]);
+            }
+        }
+    }
+    float lse_f = -INFINITY;
+    if (mx != -INFINITY) {
+        const float inv = 1.0f / sum;
+        o[0] *= inv; o[1] *= inv; o[2] *= inv; o[3] *= inv;
+        lse_f = mx + logf(sum);
+    }
+    const int64_t oi = ib * p.out_stride_b + int64_t(hq) * p.out_stride_h + 4 * lane;
+    if (p.out_dtype == BD_FP16) {
+        __half2 a = __floats2half2_rn(o[0], o[1]), b2 = __floats2half2_rn(o[2], o[3]);
+        *reinterpret_cast<uint2 *>(static_cast<__half *>(p.out) + oi) =
+            make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b2));
+    } else if (p.out_dtype == BD_BF16) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(o[0], o[1]), b2 = __floats2bfloat162_rn(o[2], o[3]);
+        *reinterpret_cast<uint2 *>(static_cast<__nv_bfloat16 *>(p.out) + oi) =
+            make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b2));
+    } else {
+        *reinterpret_cast<float4 *>(static_cast<float *>(p.out) + oi) = make_float4(o[0], o[1], o[2], o[3]);
+    }
+    if (lane == 0 && p.lse) p.lse[int64_t(ib) * p.h + hq] = lse_f;
+}
+
+cudaError_t launch_merge_parts(const DecodeParams &p, cudaStream_t stream) {
+    const int64_t rows = int64_t(p.b) * p.h;
+    bd_merge_parts_kernel<<<unsigned((rows + 3) / 4), 128, 0, stream>>>(p);
+    return cudaGetLastError();
 }
 
 // ---------------------------------------------------------------------------

@@ -204,6 +204,7 @@ struct DecodeParams {
     float *lse;                   // optional (b, h)
     int64_t out_stride_b, out_stride_h;
     int32_t out_dtype;
+    int32_t defer_merge;          // the parts of a sequence are merged by bd_merge_parts_kernel, launched next
     int32_t *status;
 };
 
@@ -227,6 +228,7 @@ struct CombinePartsParams {
 
 cudaError_t launch_pack(const PackParams &p, int bits, int group, int dtype, cudaStream_t stream);
 cudaError_t launch_prefix(const PrefixParams &p, cudaStream_t stream);
+cudaError_t launch_merge_parts(const DecodeParams &p, cudaStream_t stream);
 cudaError_t launch_decode(const DecodeParams &p, const CUtensorMap &kmap, const CUtensorMap &vmap,
                           int bits, int group, cudaStream_t stream);
 int decode_ctas_per_sm(int bits, int group, int gq);
