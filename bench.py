@@ -57,6 +57,12 @@ WORKLOADS = {
                  desc="Llama-3-70B, one KV head of 8 per GPU: b16 8q/1kv d128 s131072 4-bit g128"),
     "C5a2": dict(b=16, h=8, h_k=1, s=131072, bits=2, group=128, res=0, dtype="fp16", ragged=False, outliers=0.0,
                  desc="Llama-3-70B, one KV head of 8 per GPU: b16 8q/1kv d128 s131072 2-bit g128"),
+    # one sequence of 1 Mi tokens split along the sequence over 8 GPUs: every rank streams 131072 tokens and
+    # the ranks exchange their (out, lse) partials (all-gather over NCCL + bd_combine) inside the timed step;
+    # on fewer ranks each still holds a 131072-token shard (weak scaling of the same per-rank work)
+    "C5b": dict(b=1, h=64, h_k=8, s=131072, bits=4, group=128, res=0, dtype="fp16", ragged=False, outliers=0.0,
+                seq_split=True,
+                desc="Llama-3-70B, 1 Mi-token sequence, 131072-token shard per GPU: b1 64q/8kv d128 4-bit g128"),
 }
 
 
@@ -303,8 +309,18 @@ def main():
                                         num_splits=args.num_splits, **extras)
     workspace = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device=device)
 
+    seq_split = bool(w.get("seq_split")) and distributed
+    if seq_split:
+        from bitladder_b200 import sharding as S
+        args.eager = True                      # the step holds NCCL collectives: launched eagerly
+        sp_steps = [S.SequenceParallelStep(q, bufs[0], bufs[1], bufs[2], bufs[3], scale, w["group"], w["bits"])
+                    for bufs in caches]
+
     def step(i):
         bufs = caches[i % len(caches)]
+        if seq_split:      # partial (out, lse) of this rank's shard, all-gather, merge: every rank gets the result
+            sp_steps[i % len(sp_steps)].step()
+            return
         B.fwd_kvcache_int(q, bufs[0], bufs[1], bufs[2], bufs[3], None, scale, "k-channel", w["group"], w["bits"],
                           out=out, workspace=workspace, num_splits=args.num_splits, **extras)
 
@@ -372,7 +388,8 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     ms_per_step = ms / steps
-    value = w["b"] * world / (ms_per_step * 1e-3)
+    seqs = w["b"] * (1 if seq_split else world)          # sequences advanced per step, whole job
+    value = seqs / (ms_per_step * 1e-3)
 
     # ---- end to end: the step's inputs come from pinned host memory, the result goes back
     e2e_steps = min(steps, 500)
@@ -400,7 +417,7 @@ def main():
     out_host = torch.empty(q.shape, dtype=q.dtype).pin_memory()
     h2d = stage_host.numel() * stage_host.element_size()
     d2h = out_host.numel() * out_host.element_size()
-    e2e_runs = [] if args.no_e2e else [
+    e2e_runs = [] if (args.no_e2e or seq_split) else [
         B.DecodeStep(q_dev, bufs[0], bufs[1], bufs[2], bufs[3], None, scale, "k-channel", w["group"], w["bits"],
                      num_splits=args.num_splits, **e2e_kw) for bufs in caches]
     e2e_stream = torch.cuda.current_stream()
@@ -413,7 +430,7 @@ def main():
         e2e_stream.synchronize()                    # the caller needs the result before the next step
 
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and not seq_split:
         for i in range(3):
             e2e_step(i)
         barrier()
@@ -457,7 +474,9 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f16 (int4/int2 codes, fp32 accumulate)", "data": "synthetic",
             "config": {"workload": f"{args.workload}: {w['desc']}", "per_gpu_batch": w["b"],
-                       "global_batch": w["b"] * world, "sharding": "batch, no data-path collective",
+                       "global_batch": w["b"] * (1 if w.get("seq_split") else world),
+                       "sharding": ("sequence split: all-gather of (out, lse) partials + merge inside the step"
+                                    if seq_split else "batch, no data-path collective"),
                        "rows_per_kv_head": splits, "launch": "cuda graph replay" if graph is not None else "eager",
                        "l2": f"{args.copies} rotating packed-cache copies of {nbytes / 2**20:.0f} MiB each (> 126 MB L2)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

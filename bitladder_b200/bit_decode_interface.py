@@ -338,7 +338,7 @@ class DecodeStep:
     def __init__(self, q, k_pack, k_params, v_pack, v_params, opt_block_table=None, softmax_scale=1.0,
                  quant_mode="k-channel", group_size=128, num_bits=4, *, k_res=None, v_res=None, res_lens=None,
                  cache_seqlens=None, seqlen_k=None, return_lse=False, out=None, out_dtype=None, num_splits=0,
-                 k_new=None, v_new=None):
+                 k_new=None, v_new=None, lse=None):
         _check_config(quant_mode, group_size, num_bits)
         _check_cuda(q, k_pack, k_params, v_pack, v_params, k_res, v_res, res_lens, cache_seqlens, out,
                     opt_block_table, k_new, v_new)
@@ -349,7 +349,13 @@ class DecodeStep:
             _require(out.shape == q.shape and out.stride(-1) == 1,
                      "out must have q's shape and a contiguous last dimension")
         self.out = out
-        self.lse = torch.empty((q.shape[0], q.shape[2]), dtype=torch.float32, device=q.device) if return_lse else None
+        if lse is not None:
+            _require(lse.is_cuda and lse.dtype == torch.float32 and lse.is_contiguous() and
+                     lse.numel() == q.shape[0] * q.shape[2], "lse must be a contiguous fp32 CUDA tensor of b*h elements")
+            self.lse = lse
+        else:
+            self.lse = (torch.empty((q.shape[0], q.shape[2]), dtype=torch.float32, device=q.device)
+                        if return_lse else None)
         self._args = _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
                                   k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, self.lse, num_splits,
                                   opt_block_table, k_new, v_new)

@@ -19,10 +19,14 @@ from typing import List, Optional, Sequence, Tuple
 
 import torch
 
-from .bit_decode_interface import combine_partials, fwd_kvcache_int, pack_block_tokens
+import ctypes as C
+
+from . import _lib
+from .bit_decode_interface import (DecodeStep, _dtype_code, _stream, combine_partials, fwd_kvcache_int,
+                                   pack_block_tokens)
 
 __all__ = ["shard_range", "shard_batch", "shard_kv_heads", "sequence_shard_bounds",
-           "gather_partials", "decode_sequence_parallel"]
+           "gather_partials", "decode_sequence_parallel", "SequenceParallelStep"]
 
 
 def shard_range(n: int, rank: int, world: int) -> Tuple[int, int]:
@@ -101,3 +105,44 @@ def decode_sequence_parallel(q, k_pack, k_params, v_pack, v_params, softmax_scal
                                    out_dtype=torch.float32, return_lse=True)
     outs, lses = gather_partials(out_p, lse_p, group)
     return combine_partials(outs, lses, out_dtype=out_dtype or q.dtype, return_lse=return_lse)
+
+
+class SequenceParallelStep:
+    """``decode_sequence_parallel`` prepared once for a decoder loop: the local partial, the gathered
+    partials of all ranks and the result live in buffers allocated here, the local step is a
+    ``DecodeStep``, the exchange is ONE ``all_gather_into_tensor`` of ``b*h*(d+1)`` fp32 values per rank
+    (each rank's normalised output rows followed by their log-sum-exps) and the merge one ``bd_combine``
+    launch over pointers into the gathered buffer.  ``step()`` returns the full result on every rank."""
+
+    def __init__(self, q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size=128, num_bits=4, *,
+                 seqlen_k=None, k_res=None, v_res=None, res_lens=None, cache_seqlens=None, group=None,
+                 out_dtype=None):
+        import torch.distributed as dist
+
+        self._dist, self._group = dist, group
+        world = dist.get_world_size(group)
+        if world > _lib.BD_MAX_PARTS:
+            raise RuntimeError(f"at most {_lib.BD_MAX_PARTS} ranks can share a sequence")
+        b, _, h, d = q.shape
+        n_out, n = b * h * d, b * h * (d + 1)
+        dev = q.device
+        self._local = torch.empty(n, dtype=torch.float32, device=dev)
+        self._gathered = torch.empty(world * n, dtype=torch.float32, device=dev)
+        self._local_step = DecodeStep(q, k_pack, k_params, v_pack, v_params, None, softmax_scale, "k-channel",
+                                      group_size, num_bits, seqlen_k=seqlen_k, k_res=k_res, v_res=v_res,
+                                      res_lens=res_lens, cache_seqlens=cache_seqlens,
+                                      out=self._local[:n_out].view(b, 1, h, d), lse=self._local[n_out:])
+        self.out = torch.empty((b, 1, h, d), dtype=out_dtype or q.dtype, device=dev)
+        base = self._gathered.data_ptr()
+        self._po = (C.c_void_p * world)(*[base + 4 * (r * n) for r in range(world)])
+        self._pl = (C.c_void_p * world)(*[base + 4 * (r * n + n_out) for r in range(world)])
+        self._args = _lib.CombineArgs(n_parts=world, part_out=C.cast(self._po, C.POINTER(C.c_void_p)),
+                                      part_lse=C.cast(self._pl, C.POINTER(C.c_void_p)), rows=b * h, d=d,
+                                      out=self.out.data_ptr(), lse=None, out_dtype=_dtype_code(self.out.dtype))
+        self._dev = dev
+
+    def step(self):
+        self._local_step.step()
+        self._dist.all_gather_into_tensor(self._gathered, self._local, group=self._group)
+        _lib.check(_lib.load().bd_combine(C.byref(self._args), _stream(self._dev)), "bd_combine")
+        return self.out

@@ -54,6 +54,12 @@ def _rank_main(rank, world, port, x, ref_seq, ref_batch, bits, group, res):
                                               return_lse=True, **kw)
         err = np.abs(out.float().cpu().numpy()[:, 0] - ref_seq).max()
         assert err <= 2e-3, ("sequence split", rank, err)
+        # the same exchange prepared once (one all-gather of a packed buffer, one merge launch)
+        sp = S.SequenceParallelStep(x["q"].to(dev), *bufs, scale, group, bits, seqlen_k=n, **kw)
+        for _ in range(2):
+            out2 = sp.step()
+            err = np.abs(out2.float().cpu().numpy()[:, 0] - ref_seq).max()
+            assert err <= 2e-3, ("prepared sequence split", rank, err)
 
         # ---- batch split: rank r holds sequences [lo, hi); no communication at all
         lo, hi = S.shard_range(b, rank, world)
