@@ -27,6 +27,7 @@ Prints ONE JSON line (rank 0):
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import math
 import os
@@ -296,7 +297,8 @@ def main():
     distributed = world > 1
     if distributed:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=device)
+        # a short timeout: a rank that falls out of step must end the run, not hold the GPUs for ten minutes
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=90))
 
     warmup = max(args.warmup, 3)
     steps = max(args.steps, 1)
@@ -372,7 +374,12 @@ def main():
     # Clock pre-roll: NVML refreshes its readings every few tens of ms, so keep the
     # same kernels running for about half a second before the timed region starts.
     t_pre = time.perf_counter()
-    while not args.no_preroll and time.perf_counter() - t_pre < 0.5:
+    if seq_split and not args.no_preroll:
+        # the step holds collectives: every rank must run the SAME number of steps, so the pre-roll
+        # is a fixed count here, never a wall-clock loop
+        run_steps(3000)
+        torch.cuda.synchronize()
+    while not seq_split and not args.no_preroll and time.perf_counter() - t_pre < 0.5:
         run_steps(60)
         torch.cuda.synchronize()
     barrier()
