@@ -108,6 +108,10 @@ int plan_rows(int b, int h_k, int64_t max_s, int bits, int sm_count, int ctas_pe
     const int64_t slots = int64_t(sm_count) * ctas_per_sm;
     int64_t rows = std::max<int64_t>(1, slots / h_k);
     rows = std::min<int64_t>(rows, std::max<int64_t>(1, (int64_t(b) * nblk + 3) / 4));
+    // Small problems (every pack block can have a warp of its own with at most four CTAs per
+    // sequence): four ranges per sequence keep the merge on the in-kernel one-trip path.
+    const int64_t warps = bd::decode_warps(bits, 128, 4);
+    if (nblk <= 4 * warps) rows = std::min<int64_t>(rows, 4 * int64_t(b));
     return int(std::min<int64_t>(rows, 1 << 20));
 }
 
