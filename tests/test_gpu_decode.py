@@ -192,3 +192,23 @@ def test_two_calls_return_the_same_bits():
     for _ in range(3):
         o2, l2 = B.fwd_kvcache_int(*args, **kw)
         assert torch.equal(o1, o2) and torch.equal(l1, l2)
+
+
+@pytest.mark.parametrize("bits,dtype", [(4, "fp16"), (2, "fp16")])
+def test_many_short_ragged_sequences(bits, dtype):
+    """More sequences than CTA rows: every warp's range crosses several sequence boundaries, some
+    sequences are empty, some have only a tail, most are finished by a single warp."""
+    import bitladder_b200 as B
+    b, s, h, h_k, res = 67, 512, 16, 4, 24
+    x = H.gen_qkv(b, s, h, h_k, seed=77, dtype=dtype, res=res)
+    ref = H.oracle_pack(x["k"], x["v"], bits, 128, dtype)
+    bufs = G.pack_gpu(B, x["k"], x["v"], bits, 128)
+    g = torch.Generator().manual_seed(11)
+    cs = torch.randint(0, s + 1, (b,), generator=g, dtype=torch.int32)
+    rl = torch.randint(0, res + 1, (b,), generator=g, dtype=torch.int32)
+    cs[0], rl[0] = 0, 0            # nothing at all
+    cs[1], rl[1] = 0, res          # only a tail
+    cs[2], rl[2] = s, 0            # only packed tokens
+    cs[b - 1], rl[b - 1] = 0, 0    # empty at the very end
+    out, lse = _run(B, x, bufs, bits, 128, dtype, k_res=x["k_res"], v_res=x["v_res"], cache_seqlens=cs, res_lens=rl)
+    _check(x, ref, out, lse, bits, 128, dtype, cs, rl, res=True)
