@@ -1152,7 +1152,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 // (flash_fwd_kernel.h:1217-1231, 1280-1298).  Sequences with at most one part were finished by
 // the decode kernel itself.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) bd_merge_parts_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(128, 1) bd_merge_parts_kernel(const DecodeParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t rowid = int64_t(blockIdx.x) * 4 + warp;
     if (rowid >= int64_t(p.b) * p.h) return;
@@ -1171,35 +1171,37 @@ __global__ void __launch_bounds__(128) bd_merge_parts_kernel(const DecodeParams 
         const bool live = i < nrows && (pr.dense || row_has_part(p.part, ib, pr.c0 + i));
         return live ? __ldcg(p.part_lse + (slot0 + int64_t(i) * p.h_k) * p.gq + qrow) : -INFINITY;
     };
-    float mx = -INFINITY;
-    for (int base = 0; base < nrows; base += 32) mx = fmaxf(mx, lse_of(base + lane));
+    // Up to 32 parts at a time: lane i weighs part i, and every lane asks for its 16 bytes of all the
+    // parts of the round before any answer is used (the rows do not depend on the weights), so a
+    // round costs one trip to L2.  Rows of parts that weigh nothing are never used (select, not multiply).
+    const float ls0 = lse_of(lane);
+    float mx = ls0;
+    for (int base = 32; base < nrows; base += 32) mx = fmaxf(mx, lse_of(base + lane));
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
     float sum = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
     for (int base = 0; base < nrows; base += 32) {
-        const float ls = lse_of(base + lane);
+        const int cnt = min(32, nrows - base);
+        float4 v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (j < cnt)
+                v[j] = __ldcg(reinterpret_cast<const float4 *>(
+                    p.part_out + ((slot0 + int64_t(base + j) * p.h_k) * p.gq + qrow) * kHeadDim + 4 * lane));
+        }
+        const float ls = base == 0 ? ls0 : lse_of(base + lane);
         const float w = (ls == -INFINITY || mx == -INFINITY) ? 0.f : __expf(ls - mx);
         float t = w;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
         sum += t;
-        const int cnt = min(32, nrows - base);
-        for (int j0 = 0; j0 < cnt; j0 += 8) {
-            float4 v[8];
-            float wj[8];
 #pragma unroll
-            for (int jj = 0; jj < 8; ++jj) {
-                wj[jj] = __shfl_sync(0xffffffffu, w, (j0 + jj) & 31);
-                if (j0 + jj >= cnt) wj[jj] = 0.f;
-                v[jj] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (wj[jj] != 0.f)
-                    v[jj] = __ldcg(reinterpret_cast<const float4 *>(
-                        p.part_out + ((slot0 + int64_t(base + j0 + jj) * p.h_k) * p.gq + qrow) * kHeadDim + 4 * lane));
-            }
-#pragma unroll
-            for (int jj = 0; jj < 8; ++jj) {
-                o[0] = fmaf(wj[jj], v[jj].x, o[0]); o[1] = fmaf(wj[jj], v[jj].y, o[1]);
-                o[2] = fmaf(wj[jj], v[jj].z, o[2]); o[3] = fmaf(wj[jj], v[jj].w, o[3]);
+        for (int j = 0; j < 32; ++j) {
+            const float wj = __shfl_sync(0xffffffffu, w, j);
+            if (j < cnt && wj != 0.f) {
+                o[0] = fmaf(wj, v[j].x, o[0]); o[1] = fmaf(wj, v[j].y, o[1]);
+                o[2] = fmaf(wj, v[j].z, o[2]); o[3] = fmaf(wj, v[j].w, o[3]);
             }
         }
     }
