@@ -704,8 +704,18 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 
             // ------------------------------------------------------------ V phase
             if (!mbar_wait_bounded(vbar, phase)) { aborted = true; break; }
-#pragma unroll
+            // The two units run through the same code (a rolled loop: half the instruction bytes of
+            // the largest part of the block's code); their probabilities are picked with selects.
+#pragma unroll 1
             for (int u = 0; u < 2; ++u) {
+                uint32_t pbu[P][NQT][2];
+#pragma unroll
+                for (int j = 0; j < P; ++j)
+#pragma unroll
+                    for (int nq = 0; nq < NQT; ++nq) {
+                        pbu[j][nq][0] = u ? Pb[1][j][nq][0] : Pb[0][j][nq][0];
+                        pbu[j][nq][1] = u ? Pb[1][j][nq][1] : Pb[0][j][nq][1];
+                    }
 #pragma unroll
                 for (int j = 0; j < P; ++j) {
                     const int T0 = 16 * u + 32 * j;                       // first token of this k-slice
@@ -735,11 +745,11 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                         // from the same rounded probabilities the numerator uses)
                         constexpr uint32_t kOnes = 0x3c003c00u;
                         mma_f16(ZS[nq], ze0[0], NGD > 1 ? ze0[NGD - 1] : kOnes, ze1[0], NGD > 1 ? ze1[NGD - 1] : kOnes,
-                                Pb[u][j][nq][0], Pb[u][j][nq][1]);
+                                pbu[j][nq][0], pbu[j][nq][1]);
 #pragma unroll
                         for (int gd = 0; gd < NGD; ++gd) {
-                            pv[gd][nq][0] = hmul2_u32(Pb[u][j][nq][0], sc0[gd]);
-                            pv[gd][nq][1] = hmul2_u32(Pb[u][j][nq][1], sc1[gd]);
+                            pv[gd][nq][0] = hmul2_u32(pbu[j][nq][0], sc0[gd]);
+                            pv[gd][nq][1] = hmul2_u32(pbu[j][nq][1], sc1[gd]);
                         }
                     }
                     constexpr int NCB = (BITS == 4) ? 2 : 1;              // ldmatrix.x4 per k-slice
