@@ -145,7 +145,7 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.samples)}
 
 
-NCU_TRAFFIC_C2 = 292_400_384     # bytes per launch: 287.498 MB read + 4.902 MB written
+NCU_TRAFFIC_C2 = 291_537_920     # bytes per launch: 287.490 MB read + 4.048 MB written
 NCU_ALGO_C2 = 287_440_896        # algorithmic bytes of the same launch
 
 # ---------------------------------------------------------------------------
