@@ -27,6 +27,31 @@ __device__ __forceinline__ float2 pair_to_float2(uint32_t w) {
     }
 }
 
+// Running min / max of packed pairs in their own format (exact: no rounding is involved, and a
+// NaN operand yields the other operand, like fminf / fmaxf).  +inf / -inf as the neutral starts.
+template <bool BF16>
+__device__ __forceinline__ uint32_t pair_min(uint32_t a, uint32_t b) {
+    if constexpr (BF16) {
+        __nv_bfloat162 r = __hmin2(*reinterpret_cast<__nv_bfloat162 *>(&a), *reinterpret_cast<__nv_bfloat162 *>(&b));
+        return *reinterpret_cast<uint32_t *>(&r);
+    } else {
+        __half2 r = __hmin2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
+        return *reinterpret_cast<uint32_t *>(&r);
+    }
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t pair_max(uint32_t a, uint32_t b) {
+    if constexpr (BF16) {
+        __nv_bfloat162 r = __hmax2(*reinterpret_cast<__nv_bfloat162 *>(&a), *reinterpret_cast<__nv_bfloat162 *>(&b));
+        return *reinterpret_cast<uint32_t *>(&r);
+    } else {
+        __half2 r = __hmax2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
+        return *reinterpret_cast<uint32_t *>(&r);
+    }
+}
+template <bool BF16> constexpr uint32_t kPairPosInf = BF16 ? 0x7f807f80u : 0x7c007c00u;
+template <bool BF16> constexpr uint32_t kPairNegInf = BF16 ? 0xff80ff80u : 0xfc00fc00u;
+
 // roundf(v) for v = (x - mn) * scale_inv, left in the mantissa of a float: one add.
 //   v lies in [0, maxv + 1e-6] (x >= mn, and (mx - mn) * fl(maxv / (mx - mn)) exceeds maxv by a few
 //   ulps at most), or is NaN (NaN or infinite inputs), which fmaxf turns into 0 exactly like the
@@ -97,20 +122,24 @@ bd_pack_kernel(const PackParams p) {
                 raw[pi][j] = __ldg(reinterpret_cast<const unsigned int *>(kbase + t * p.k_stride_s));
             }
         float mn[NGK][2], mx[NGK][2];
+        {
+            uint32_t pmn[NGK], pmx[NGK];        // both channels at once, in the input format
 #pragma unroll
-        for (int gk = 0; gk < NGK; ++gk) {
-            mn[gk][0] = mn[gk][1] = INFINITY;
-            mx[gk][0] = mx[gk][1] = -INFINITY;
-        }
+            for (int gk = 0; gk < NGK; ++gk) { pmn[gk] = kPairPosInf<BF16>; pmx[gk] = kPairNegInf<BF16>; }
 #pragma unroll
-        for (int pi = 0; pi < PPT; ++pi)
+            for (int pi = 0; pi < PPT; ++pi)
 #pragma unroll
-            for (int j = 0; j < P; ++j) {
-                const float2 x = pair_to_float2<BF16>(raw[pi][j]);
-                const int gk = j / FPG;
-                mn[gk][0] = fminf(mn[gk][0], x.x); mx[gk][0] = fmaxf(mx[gk][0], x.x);
-                mn[gk][1] = fminf(mn[gk][1], x.y); mx[gk][1] = fmaxf(mx[gk][1], x.y);
+                for (int j = 0; j < P; ++j) {
+                    const int gk = j / FPG;
+                    pmn[gk] = pair_min<BF16>(pmn[gk], raw[pi][j]);
+                    pmx[gk] = pair_max<BF16>(pmx[gk], raw[pi][j]);
+                }
+#pragma unroll
+            for (int gk = 0; gk < NGK; ++gk) {
+                const float2 a = pair_to_float2<BF16>(pmn[gk]), b2 = pair_to_float2<BF16>(pmx[gk]);
+                mn[gk][0] = a.x; mn[gk][1] = a.y; mx[gk][0] = b2.x; mx[gk][1] = b2.y;
             }
+        }
 #pragma unroll
         for (int gk = 0; gk < NGK; ++gk) {
             red[T][gk][0][2 * cp] = mn[gk][0]; red[T][gk][0][2 * cp + 1] = mn[gk][1];
@@ -191,17 +220,25 @@ bd_pack_kernel(const PackParams p) {
         for (int u = 0; u < VITER; ++u) {
             const int t = u * TPI + tsub;
             float mn[NGD], mx[NGD];
+            {
+                uint32_t pmn[NGD], pmx[NGD];
 #pragma unroll
-            for (int gd = 0; gd < NGD; ++gd) { mn[gd] = INFINITY; mx[gd] = -INFINITY; }
+                for (int gd = 0; gd < NGD; ++gd) { pmn[gd] = kPairPosInf<BF16>; pmx[gd] = kPairNegInf<BF16>; }
 #pragma unroll
-            for (int j = 0; j < P; ++j) {
-                const int gd = j / FPGV;
-                const uint32_t w4[4] = {raw[u][j].x, raw[u][j].y, raw[u][j].z, raw[u][j].w};
+                for (int j = 0; j < P; ++j) {
+                    const int gd = j / FPGV;
+                    const uint32_t w4[4] = {raw[u][j].x, raw[u][j].y, raw[u][j].z, raw[u][j].w};
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const float2 x = pair_to_float2<BF16>(w4[r]);
-                    mn[gd] = fminf(mn[gd], fminf(x.x, x.y));
-                    mx[gd] = fmaxf(mx[gd], fmaxf(x.x, x.y));
+                    for (int r = 0; r < 4; ++r) {
+                        pmn[gd] = pair_min<BF16>(pmn[gd], w4[r]);
+                        pmx[gd] = pair_max<BF16>(pmx[gd], w4[r]);
+                    }
+                }
+#pragma unroll
+                for (int gd = 0; gd < NGD; ++gd) {
+                    const float2 a = pair_to_float2<BF16>(pmn[gd]), b2 = pair_to_float2<BF16>(pmx[gd]);
+                    mn[gd] = fminf(a.x, a.y);
+                    mx[gd] = fmaxf(b2.x, b2.y);
                 }
             }
             float sinv[NGD];
