@@ -121,11 +121,13 @@ typedef struct bd_decode_args {
     int64_t k_pack_stride_b, k_params_stride_b, v_pack_stride_b;
     int64_t v_params_stride_b, v_params_stride_g, v_params_stride_h;
     const int32_t *cache_seqlens;   /* optional (b): quantized tokens valid per sequence */
-    const void *k_res;        /* optional (b, res_cap, h_k, d), same dtype as q */
+    const void *k_res;        /* optional (b, res_len, h_k, d), same dtype as q; with k_new the step also
+                                 WRITES row res_lens[ib] of k_res and v_res (see k_new below) */
     const void *v_res;
     int64_t res_stride_b, res_stride_s, res_stride_h;
     const int32_t *res_lens;  /* optional (b): tail tokens valid per sequence */
-    int32_t res_len;          /* tail length when res_lens is null (0 = no tail) */
+    int32_t res_len;          /* token rows of the tail buffers (at most 256): the tail length of every
+                                 sequence when res_lens is null, the bound of res_lens[ib] otherwise */
     int32_t b, h, h_k, d;
     int32_t s;                /* quantized tokens (upper bound when cache_seqlens is given) */
     int32_t s_cap;            /* token capacity of the pack buffers, a multiple of NB */
