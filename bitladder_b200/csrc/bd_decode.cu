@@ -568,7 +568,11 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             // step per block), one of a 2-bit block (its 8 fields fill the registers).
             constexpr int UG = (P == 4) ? 2 : 1;
             uint32_t Pb[2][P][NQT][2];      // probabilities as B fragments (fp16), per unit and field
-#pragma unroll
+            // One group at 4 bits.  At 2 bits two groups: with G=64 they run through the same
+            // (rolled) code, which measured 3 % faster there (the block body is about 50 KB and
+            // instruction fetch is that kernel's largest stall) and 2.5 % slower with G=128.
+            constexpr int kGroupUnroll = (UG == 1 && GROUP == 64) ? 1 : 2;
+#pragma unroll kGroupUnroll
             for (int ug = 0; ug < 2 / UG; ++ug) {
                 float S[UG][P][NQT][4];
 #pragma unroll
@@ -678,20 +682,26 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                         const float f1 = __shfl_sync(0xffffffffu, f[1], g >> 1);
                         const float fq = (g & 1) ? f1 : f0;
                         const uint32_t fh = pack_f16x2(fq, fq);
+                        // (only reached with one unit per group: the earlier unit is unit 0)
 #pragma unroll
-                        for (int up = 0; up < ug * UG; ++up)
-#pragma unroll
-                            for (int j = 0; j < P; ++j) {
-                                Pb[up][j][nq][0] = hmul2_u32(Pb[up][j][nq][0], fh);
-                                Pb[up][j][nq][1] = hmul2_u32(Pb[up][j][nq][1], fh);
-                            }
+                        for (int j = 0; j < P; ++j) {
+                            Pb[0][j][nq][0] = hmul2_u32(Pb[0][j][nq][0], fh);
+                            Pb[0][j][nq][1] = hmul2_u32(Pb[0][j][nq][1], fh);
+                        }
                     }
 #pragma unroll
                     for (int uu = 0; uu < UG; ++uu)
 #pragma unroll
                         for (int j = 0; j < P; ++j) {
-                            Pb[ug * UG + uu][j][nq][0] = movmatrix_trans(pack_f16x2(t[uu * P + j][0], t[uu * P + j][1]));
-                            Pb[ug * UG + uu][j][nq][1] = movmatrix_trans(pack_f16x2(t[uu * P + j][2], t[uu * P + j][3]));
+                            const uint32_t p0 = movmatrix_trans(pack_f16x2(t[uu * P + j][0], t[uu * P + j][1]));
+                            const uint32_t p1 = movmatrix_trans(pack_f16x2(t[uu * P + j][2], t[uu * P + j][3]));
+                            if constexpr (UG == 2) {
+                                Pb[uu][j][nq][0] = p0; Pb[uu][j][nq][1] = p1;
+                            } else if (ug == 0) {          // a runtime index when the group loop is rolled
+                                Pb[0][j][nq][0] = p0; Pb[0][j][nq][1] = p1;
+                            } else {
+                                Pb[1][j][nq][0] = p0; Pb[1][j][nq][1] = p1;
+                            }
                         }
                 }
             }
