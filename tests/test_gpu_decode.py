@@ -34,6 +34,8 @@ def _check(x, ref, out, lse, bits, group, dtype, cs=None, rl=None, res=False):
     (4, 128, 32, 8, 1024, 1), (4, 128, 8, 8, 512, 2), (2, 128, 32, 8, 2048, 0), (4, 64, 32, 8, 1024, 0),
     (2, 64, 32, 8, 2048, 0), (4, 128, 64, 8, 1024, 0), (4, 128, 32, 2, 1024, 0), (4, 128, 24, 8, 1024, 3),
     (2, 128, 40, 8, 512, 0), (4, 128, 2, 2, 128, 0),
+    (4, 128, 160, 160, 256, 0),    # more KV heads than SMs: one CTA row, the grid runs in more than one wave
+    (2, 128, 320, 160, 512, 0),
 ])
 def test_decode_matches_oracle(bits, group, h, h_k, s, splits):
     import bitladder_b200 as B
