@@ -247,6 +247,10 @@ def run_reference(args, w, rank):
         return
     steps = max(1, min(args.steps, 20))
     warmup = max(1, min(args.warmup, 3))
+    if args.gpus > 1:
+        # torchrun exports OMP_NUM_THREADS=1 to its ranks; the one rank that runs this arm takes the host's cores
+        from oracle import c_oracle
+        c_oracle.set_num_threads(len(os.sched_getaffinity(0)))
     tps, sec, cores, sample = cpu_sample(w, 1000, steps, warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus,

@@ -56,6 +56,16 @@ static inline uint16_t f2bf(float x) {           /* round to nearest even */
 }
 static inline float in2f(uint16_t bits, int is_bf16) { return is_bf16 ? bf2f(bits) : h2f(bits); }
 
+/* Threads the parallel loops will use from now on (n <= 0: leave as is).  A launcher that
+   exports OMP_NUM_THREADS=1 for its ranks would otherwise pin the timed CPU baseline to one core. */
+void bdo_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int bdo_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -50,6 +50,13 @@ def num_threads() -> int:
     return int(lib().bdo_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    """Use ``n`` OpenMP threads from now on (overrides an ``OMP_NUM_THREADS`` inherited from a launcher)."""
+    f = lib().bdo_set_num_threads
+    f.argtypes, f.restype = [ctypes.c_int], None
+    f(int(n))
+
+
 def quantize_pack(k, v, bits: int, group: int, dtype: str = "fp16"):
     k16, v16 = _bits16(k), _bits16(v)
     b, s, h, d = k16.shape
