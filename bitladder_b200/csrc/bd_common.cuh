@@ -43,11 +43,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after ~kSpinLimit polls (each poll blocks for a
-// hardware-defined slice, then backs off) and reports false.
+// Bounded wait: gives up after `limit` polls (each poll blocks for a
+// hardware-defined slice, then backs off) and reports false.  kSpinLimit is the default.
 constexpr uint32_t kSpinLimit = 1u << 22;
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit = kSpinLimit) {
+    for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if (it > 64) __nanosleep(64);
     }

@@ -50,6 +50,22 @@
 
 namespace bd {
 
+#ifdef BD_TRACE
+// Timing trace for development builds only (-DBD_TRACE): per CTA its SM, start, the time every warp
+// left the streaming loop, and the CTA's end, in nanoseconds of the global timer.
+__device__ unsigned long long g_trace[4096 * 16];
+__device__ __forceinline__ unsigned long long trace_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ unsigned trace_smid() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %smid;" : "=r"(r));
+    return r;
+}
+#endif
+
 #ifndef BD_MAX_WARPS
 #define BD_MAX_WARPS 12
 #endif
@@ -255,6 +271,12 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int ih = blockIdx.x % p.h_k, row = blockIdx.x / p.h_k;
     const int g = lane >> 2, l = lane & 3;
+#ifdef BD_TRACE
+    if (tid == 0 && blockIdx.x < 4096) {
+        g_trace[blockIdx.x * 16 + 0] = trace_smid();
+        g_trace[blockIdx.x * 16 + 1] = trace_now();
+    }
+#endif
     if ((smem_base & 1023u) != 0) {                      // never seen; refuse rather than read garbage
         if (tid == 0) atomicExch(p.status, BD_ERR_ALIGNMENT);
         return;
@@ -287,16 +309,22 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     // Paged cache: block `blk` of sequence `ib` sits in page block_table[ib][blk / blocks_per_page]
     // at block blk % blocks_per_page; the page takes the place of the batch index in every address
     // below (pages are laid out exactly like the sequences of a contiguous cache).
-    auto resolve = [&](int &ib, int &blk) {
-        if (p.block_table != nullptr) {
-            const int pg = blk / p.blocks_per_page;
-            blk -= pg * p.blocks_per_page;
-            ib = p.block_table[int64_t(ib) * p.block_table_stride + pg];
-        }
+    // A page index outside the pool is never used as an address: the copy then reads page 0
+    // (in bounds), the block is masked where it is consumed and the status word reports it.
+    auto resolve = [&](int &ib, int &blk) -> bool {
+        if (p.block_table == nullptr) return true;
+        const int pg = blk / p.blocks_per_page;
+        blk -= pg * p.blocks_per_page;
+        const int page = p.block_table[int64_t(ib) * p.block_table_stride + pg];
+        const bool ok = page >= 0 && page < p.num_pages;
+        ib = ok ? page : 0;
+        return ok;
     };
+    bool starve = p.test_starve != 0 && blockIdx.x == 0 && warp == 0;     // test hook, first copy only
     auto issue_k = [&](int ib, int blk) {
         resolve(ib, blk);
-        mbar_arrive_expect_tx(kbar, C::CODE_BYTES + PRM);
+        mbar_arrive_expect_tx(kbar, C::CODE_BYTES + PRM + (starve ? 16 : 0));
+        starve = false;
         const int row0 = ib * p.k_batch_rows + blk * 32;
         tma_load_2d(kcode, &kmap, kbar, ih * kHeadDim, row0);
         tma_load_2d(kcode + 4096, &kmap, kbar, ih * kHeadDim + 64, row0);
@@ -373,12 +401,12 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
         int seqlen = p.s;
         if (p.cache_seqlens) seqlen = min(max(p.cache_seqlens[ib], 0), p.s);
         int res_n = 0;                                // tail tokens of this sequence
-        if (p.k_res != nullptr) res_n = min(max(p.res_lens ? p.res_lens[ib] : p.res_len, 0), kTailMax);
+        if (p.k_res != nullptr) res_n = min(max(p.res_lens ? p.res_lens[ib] : p.res_len, 0), min(kTailMax, p.res_cap));
         // Fused append: the token of this step is tail row res_old.  It is read from k_new / v_new
         // (nobody reads that row of the tail buffers during this launch) and the warp that streams
         // it also stores it there, for the steps to come.
         const int res_old = res_n;
-        const bool has_new = p.k_new != nullptr && res_n < kTailMax;
+        const bool has_new = p.k_new != nullptr && res_n < min(kTailMax, p.res_cap);
         if (has_new) res_n += 1;
         // this warp's units of the sequence: pack blocks [blk0, blk1), tail tokens [tail0, tail1)
         const int nblk = (seqlen + NB - 1) / NB;
@@ -528,10 +556,18 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
         }
 
         for (int blk = blk0; blk < blk1 && !aborted; ++blk) {
-            const bool need_mask = (blk + 1) * NB > seqlen;
+            int seqlen_blk = seqlen;              // tokens of the sequence this block may use
+            if (p.block_table != nullptr) {
+                int pib = ib, pblk = blk;
+                if (!resolve(pib, pblk)) {        // page index outside the pool: the whole block is masked
+                    seqlen_blk = blk * NB;
+                    if (lane == 0) atomicExch(p.status, BD_ERR_INVALID);
+                }
+            }
+            const bool need_mask = (blk + 1) * NB > seqlen_blk;
 
             // ------------------------------------------------------------ K phase
-            if (!mbar_wait_bounded(kbar, phase)) { aborted = true; break; }
+            if (!mbar_wait_bounded(kbar, phase, p.spin_limit)) { aborted = true; break; }
 
             // q . zero per token group (rows of the A operand all equal the zero vector)
             float Zc[NGK][NQT][2];
@@ -671,7 +707,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) {
                                     const int tok = blk * NB + 16 * (ug * UG + uu) + 32 * j + g + 8 * (e >> 1);
-                                    if (tok >= seqlen) t[uu * P + j][e] = -INFINITY;
+                                    if (tok >= seqlen_blk) t[uu * P + j][e] = -INFINITY;
                                 }
                     }
                     float f[2];
@@ -713,7 +749,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             }
 
             // ------------------------------------------------------------ V phase
-            if (!mbar_wait_bounded(vbar, phase)) { aborted = true; break; }
+            if (!mbar_wait_bounded(vbar, phase, p.spin_limit)) { aborted = true; break; }
             // The two units run through the same code (a rolled loop: half the instruction bytes of
             // the largest part of the block's code); their probabilities are picked with selects.
 #pragma unroll 1
@@ -742,8 +778,8 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                     }
                     if (need_mask) {          // params of tokens past the end may be uninitialised
                         const int tok = blk * NB + r0;
-                        const uint32_t k0 = (tok < seqlen ? 0x0000ffffu : 0u) | (tok + 1 < seqlen ? 0xffff0000u : 0u);
-                        const uint32_t k1 = (tok + 8 < seqlen ? 0x0000ffffu : 0u) | (tok + 9 < seqlen ? 0xffff0000u : 0u);
+                        const uint32_t k0 = (tok < seqlen_blk ? 0x0000ffffu : 0u) | (tok + 1 < seqlen_blk ? 0xffff0000u : 0u);
+                        const uint32_t k1 = (tok + 8 < seqlen_blk ? 0x0000ffffu : 0u) | (tok + 9 < seqlen_blk ? 0xffff0000u : 0u);
 #pragma unroll
                         for (int gd = 0; gd < NGD; ++gd) { sc0[gd] &= k0; ze0[gd] &= k0; sc1[gd] &= k1; ze1[gd] &= k1; }
                     }
@@ -803,6 +839,9 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             phase ^= 1;
         }
         if (aborted) *abort_flag = 1;
+#ifdef BD_TRACE
+        if (lane == 0 && blockIdx.x < 4096 && warp < 13) g_trace[blockIdx.x * 16 + 2 + warp] = trace_now();
+#endif
 
         // ------------------------------------------------------------------
         // End of this warp's share of the sequence.  The warps of the CTA whose ranges
@@ -1155,6 +1194,9 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     // after the stream: error exit
     // ======================================================================
     __syncthreads();
+#ifdef BD_TRACE
+    if (tid == 0 && blockIdx.x < 4096) g_trace[blockIdx.x * 16 + 15] = trace_now();
+#endif
     if (*abort_flag != 0) {
         if (tid == 0) atomicExch(p.status, BD_ERR_TIMEOUT);
         // give copies that are still in flight time to land before the block's
@@ -1246,6 +1288,12 @@ __global__ void __launch_bounds__(128, 1) bd_merge_parts_kernel(const DecodePara
     if (lane == 0 && p.lse) p.lse[int64_t(ib) * p.h + hq] = lse_f;
 }
 
+#ifdef BD_TRACE
+extern "C" int bd_trace_read(void *dst, size_t bytes) {
+    return int(cudaMemcpyFromSymbol(dst, g_trace, bytes < sizeof(g_trace) ? bytes : sizeof(g_trace)));
+}
+#endif
+
 cudaError_t launch_merge_parts(const DecodeParams &p, cudaStream_t stream) {
     const int64_t rows = int64_t(p.b) * p.h;
     bd_merge_parts_kernel<<<unsigned((rows + 3) / 4), 128, 0, stream>>>(p);
@@ -1264,7 +1312,7 @@ __global__ void __launch_bounds__(256) bd_prefix_kernel(const PrefixParams p) {
     int32_t sum = 0;
     auto units = [&](int i) {
         return seq_blocks(p.cache_seqlens ? p.cache_seqlens[i] : p.s, p.s, p.block_tokens) +
-               tail_chunks((p.res_lens ? p.res_lens[i] : p.res_len) + p.res_extra);
+               tail_chunks(min(max(p.res_lens ? p.res_lens[i] : p.res_len, 0), p.res_len) + p.res_extra);
     };
     for (int i = lo; i < hi; ++i) sum += units(i);
     partial[tid] = sum;

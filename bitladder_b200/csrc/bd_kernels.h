@@ -181,6 +181,7 @@ struct DecodeParams {
     const int32_t *cache_seqlens;
     const int32_t *block_table;   // paged cache: [b][block_table_stride] page indices; null: contiguous
     int32_t block_table_stride, blocks_per_page;
+    int32_t num_pages;            // pages the packed buffers hold (page indices outside [0, num_pages) are refused)
     const void *k_res, *v_res;
     void *k_res_out, *v_res_out;  // the same buffers, written by the fused append
     const void *k_new, *v_new;    // (b, 1, h_k, d): this step's token, appended to the tail; null: no append
@@ -205,6 +206,8 @@ struct DecodeParams {
     int64_t out_stride_b, out_stride_h;
     int32_t out_dtype;
     int32_t defer_merge;          // the parts of a sequence are merged by bd_merge_parts_kernel, launched next
+    uint32_t spin_limit;          // polls a wait on a copy may take before the warp gives up
+    int32_t test_starve;          // test hook: warp 0 of CTA 0 expects 16 bytes more than its first copy brings
     int32_t *status;
 };
 
@@ -212,7 +215,7 @@ struct PrefixParams {
     const int32_t *cache_seqlens;     // null: every sequence has s tokens
     const int32_t *res_lens;          // null: every sequence has res_len tail tokens
     int32_t *table;
-    int32_t b, s, block_tokens, res_len;
+    int32_t b, s, block_tokens, res_len;   // res_len: rows the tail buffers hold (per-sequence lengths are clamped to it)
     int32_t res_extra;                // 1 when the step appends a token to every tail
 };
 

@@ -3,8 +3,15 @@
  * called from the shipped library; used by the tests as a second, independent
  * statement of the formulas and by the benchmark's cpu_baseline leg).
  *
- * Parity status: unpinned at the element level — the reference has no golden
- * vectors and no CPU path; see oracle/oracle.py for what anchors it.
+ * Parity status: pinned for 4-bit, group 128 and 32.  The reference has no CPU path and no
+ * golden vectors of its own, but its CUDA kernels compile for sm_100a (oracle/build_ref.py);
+ * what they write on seeded inputs is committed as tests/golden/ref_i4.npz
+ * (tests/golden/make_ref_golden.py) and this restatement reproduces the packed codes, scales and
+ * zeros of the reference built WITHOUT --use_fast_math byte for byte (tests/test_ref_golden.py).
+ * The reference as shipped (--use_fast_math, setup.py:149) divides with the GPU's approximate
+ * reciprocal; its scale_inv differs by one ulp in about a quarter of the groups, which moves a
+ * code by one step where (x - min) * 15 / range is exactly k + 0.5 (a few codes in 10^5).
+ * 2-bit, group 64 and bf16 have no runnable reference kernel: defined by this build.
  *
  * Restates (paths relative to the reference project):
  *   quantizer        csrc/bit_decode/src/include/qpack.h:219-300, :110-217
@@ -74,6 +81,24 @@ int bdo_num_threads(void) {
 #endif
 }
 
+/*
+ * Where the scale of (group g of a pack block or 128-token run, element c of 0..127) is stored:
+ * `row` among the block's / run's parameter rows and fp16 column `col` (the zero sits 128 columns
+ * on).  For K, g is the token group and c the channel; for V, g is the dim group and c the token
+ * within its run of 128, and "row" selects the dim-group plane of v_params.
+ * Natural order everywhere except 4-bit with group 32, where the reference stores the parameters
+ * in the order its MMA fragments hold them (flash_fwd_kernel.h:939-957 with num_params = 4).
+ */
+static inline void param_slot(int bits, int group, int g, int c, int *row, int *col) {
+    if (bits == 4 && group == 32) {
+        *row = 2 * (g & 1) + ((c >> 3) & 1);
+        *col = 16 * (c >> 4) + 8 * (g >> 1) + (c & 7);
+    } else {
+        *row = g;
+        *col = c;
+    }
+}
+
 /* One group: min/max -> scale_inv, stored scale and zero -> codes (qpack.h:241-281). */
 static void quantize_group(const float *x, int n, int bits, uint8_t *codes,
                            uint16_t *scale_h, uint16_t *zero_h) {
@@ -129,10 +154,12 @@ int bdo_quantize_pack(const uint16_t *k, const uint16_t *v, int is_bf16,
                 }
                 uint16_t sc, ze;
                 quantize_group(xs, group, bits, cs, &sc, &ze);
-                const int64_t gi = ((int64_t)blk * NB + g0) / group;
+                int prow, pcol;
+                param_slot(bits, group, g0 / group, c, &prow, &pcol);
+                const int64_t gi = (int64_t)blk * (NB / group) + prow;
                 uint16_t *prm = k_params + (((int64_t)ib * ngk + gi) * h + ih) * 2 * d;
-                prm[c] = sc;
-                prm[d + c] = ze;
+                prm[pcol] = sc;
+                prm[d + pcol] = ze;
                 memcpy(codes_blk + g0, cs, group);
             }
             for (int p = 0; p < 32; ++p) {
@@ -151,10 +178,12 @@ int bdo_quantize_pack(const uint16_t *k, const uint16_t *v, int is_bf16,
                 uint16_t sc, ze;
                 quantize_group(xs, group, bits, cs, &sc, &ze);
                 memcpy(codes_tok + gd * group, cs, group);
-                uint16_t *prm = v_params + (((int64_t)ib * ngd + gd) * h + ih) * 2 * (int64_t)s;
-                const int64_t tb = t / 128, r = t % 128;
-                prm[256 * tb + r] = sc;
-                prm[256 * tb + 128 + r] = ze;
+                int prow, pcol;
+                param_slot(bits, group, gd, (int)(t % 128), &prow, &pcol);
+                uint16_t *prm = v_params + (((int64_t)ib * ngd + prow) * h + ih) * 2 * (int64_t)s;
+                const int64_t tb = t / 128;
+                prm[256 * tb + pcol] = sc;
+                prm[256 * tb + 128 + pcol] = ze;
             }
             for (int p = 0; p < dP; ++p) {
                 uint16_t w = 0;
@@ -210,19 +239,24 @@ int bdo_decode(const uint16_t *q, int is_bf16,
             if (t < n) {
                 const int blk = t / NB, tt = t % NB, p = tt % 32, j = tt / 32;
                 const uint16_t *kp = k_pack + (((int64_t)ib * (s / P) + (int64_t)blk * 32 + p) * h_k + ih) * d;
-                const uint16_t *kprm = k_params + (((int64_t)ib * ngk + t / group) * h_k + ih) * 2 * d;
                 for (int c = 0; c < d; ++c) {
                     const unsigned code = (kp[c] >> (bits * j)) & mask;
-                    uint16_t hv = d2h((double)code * (double)h2f(kprm[c]) + (double)h2f(kprm[d + c]));
+                    int prow, pcol;
+                    param_slot(bits, group, tt / group, c, &prow, &pcol);
+                    const uint16_t *kprm = k_params +
+                        (((int64_t)ib * ngk + (int64_t)blk * (NB / group) + prow) * h_k + ih) * 2 * d;
+                    uint16_t hv = d2h((double)code * (double)h2f(kprm[pcol]) + (double)h2f(kprm[d + pcol]));
                     krow[c] = is_bf16 ? bf2f(f2bf(h2f(hv))) : h2f(hv);
                 }
                 const uint16_t *vp = v_pack + (((int64_t)ib * s + t) * h_k + ih) * dP;
                 for (int c = 0; c < d; ++c) {
                     const unsigned code = (vp[c % dP] >> (bits * (c / dP))) & mask;
-                    const uint16_t *vprm = v_params + (((int64_t)ib * ngd + c / group) * h_k + ih) * 2 * (int64_t)s;
-                    const int64_t tb = t / 128, rr = t % 128;
-                    uint16_t hv = d2h((double)code * (double)h2f(vprm[256 * tb + rr]) +
-                                      (double)h2f(vprm[256 * tb + 128 + rr]));
+                    int prow, pcol;
+                    param_slot(bits, group, c / group, t % 128, &prow, &pcol);
+                    const uint16_t *vprm = v_params + (((int64_t)ib * ngd + prow) * h_k + ih) * 2 * (int64_t)s;
+                    const int64_t tb = t / 128;
+                    uint16_t hv = d2h((double)code * (double)h2f(vprm[256 * tb + pcol]) +
+                                      (double)h2f(vprm[256 * tb + 128 + pcol]));
                     vrow[c] = is_bf16 ? bf2f(f2bf(h2f(hv))) : h2f(hv);
                 }
             } else {

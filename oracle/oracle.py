@@ -5,15 +5,23 @@ module; it exists so the tests, the smoke check and the CPU-baseline leg of the
 benchmark can compare the CUDA kernels against an independent restatement of
 the reference algorithm.
 
-Parity status: *unpinned at the element level*.  The reference ships no golden
-vectors, known-answer tests or fixtures for this path, and it has no CPU
-implementation, so it cannot be executed without a GPU.  The restatement is
-anchored instead on (a) hand-computed known-answer cases of the quantizer
-formula, (b) an independent C restatement of the same formulas
+Parity status: *pinned for 4-bit, group 128 and 32*.  The reference has no CPU
+implementation and ships no golden vectors, but its CUDA kernels compile for
+sm_100a (``oracle/build_ref.py``); what they write on seeded inputs on a B200 is
+committed as ``tests/golden/ref_i4.npz`` (``tests/golden/make_ref_golden.py``).
+``tests/test_ref_golden.py`` checks this restatement against those bytes: packed
+codes, scales and zeros equal the reference built without ``--use_fast_math`` byte
+for byte (a group minimum of -0.0 may come out as +0.0); against the reference as
+shipped (``--use_fast_math``: the GPU's approximate reciprocal gives a
+``scale_inv`` that is one ulp off in about a quarter of the groups) codes differ
+only where ``(x - min) * 15 / range`` is exactly ``k + 0.5``, by one step.  The
+attention output agrees with the reference decode kernel's to 1e-4 on those
+inputs.  2-bit, group 64 and bf16 have no runnable reference kernel (the 2-bit V
+packer indexes past its fragment): those are defined by this build and anchored
+on (a) hand-computed known-answer cases, (b) the independent C restatement
 (``oracle/bd_oracle.c``) that must agree bit for bit, and (c) the one aggregate
-number the reference records (mean-abs error 0.002773 against fp16 attention,
-``benchmark/bench_single_decode.ipynb:92``), which this code reproduces
-statistically.
+the reference records (mean-abs error 0.002773 against fp16 attention,
+``benchmark/bench_single_decode.ipynb:92``), reproduced statistically.
 
 Reference files restated here (paths relative to the reference project):
 
@@ -41,9 +49,14 @@ pack block, ``G`` = group size, ``d`` = head dim):
   256*tb+256]`` the zeros of tokens ``128*tb ... 128*tb+127`` for dim group
   ``gd`` (``G`` consecutive dims).
 
-For 4-bit / G=128 these are byte-identical to what the reference kernels write.
-The 2-bit and G=64 layouts are defined by this build (the reference's 2-bit V
-packer is not usable and it has no G=64 instantiation).
+For 4-bit with G=128 and G=32 these are byte-identical to what the reference
+kernels write.  With 4-bit / G=32 the reference stores the parameters in the order
+its MMA fragments hold them (``flash_fwd_kernel.h:939-957`` with ``num_params = 4``):
+the scale of (group ``g`` of the pack block / 128-token run, element ``c``) sits in
+parameter row ``2*(g%2) + (c//8)%2`` at fp16 column ``16*(c//16) + 8*(g//2) + c%8``
+(see ``param_slots``).  The 2-bit and G=64 layouts are defined by this build (the
+reference's 2-bit V packer is not usable and it has no G=64 instantiation) and use
+the natural order.
 """
 from __future__ import annotations
 
@@ -52,7 +65,7 @@ import numpy as np
 __all__ = [
     "pack_block_tokens", "bf16_bits_to_f32", "f32_to_bf16_bits", "to_f32",
     "quantize_kv", "pack_k", "pack_v", "pack_k_params", "pack_v_params",
-    "unpack_k", "unpack_v", "unpack_k_params", "unpack_v_params",
+    "unpack_k", "unpack_v", "unpack_k_params", "unpack_v_params", "param_slots",
     "quantize_pack", "dequantize", "decode_attention", "combine_partials",
     "decode_from_packed",
 ]
@@ -192,19 +205,56 @@ def unpack_v(v_pack: np.ndarray, bits: int) -> np.ndarray:
     return out.reshape(b, s, h, P * dp)
 
 
-def pack_k_params(k_scale: np.ndarray, k_zero: np.ndarray) -> np.ndarray:
+def param_slots(bits: int, group: int):
+    """Index arrays ``(row, col)`` of shape (4, 128) for the 4-bit / group-32 parameter order of
+    the reference (``flash_fwd_kernel.h:939-957``), or ``None`` where the order is the natural one:
+    the scale of (group ``g`` of a block or run, element ``c``) is stored in row ``row[g, c]`` at
+    fp16 column ``col[g, c]``."""
+    if not (bits == 4 and group == 32):
+        return None
+    g = np.arange(4)[:, None]
+    c = np.arange(128)[None, :]
+    return 2 * (g % 2) + (c // 8) % 2 + 0 * c, 16 * (c // 16) + 8 * (g // 2) + c % 8
+
+
+def pack_k_params(k_scale: np.ndarray, k_zero: np.ndarray, bits: int = 4, group: int = 128) -> np.ndarray:
     """(b, s/G, h, d) fp16 x2 -> (b, s/G, h, d) float32-typed storage."""
+    slots = param_slots(bits, group)
+    if slots is not None:
+        row, col = slots
+        b, ng, h, d = k_scale.shape
+        out = []
+        for t in (k_scale, k_zero):
+            src = t.reshape(b, ng // 4, 4, h, d)
+            dst = np.empty_like(src)
+            for g in range(4):
+                dst[:, :, row[g], :, col[g]] = np.moveaxis(src[:, :, g], -1, 0)
+            out.append(dst.reshape(b, ng, h, d))
+        k_scale, k_zero = out
     both = np.concatenate([k_scale, k_zero], axis=-1).astype(np.float16)   # (b, ng, h, 2d)
     return np.ascontiguousarray(both).view(np.float32)
 
 
-def unpack_k_params(k_params: np.ndarray):
+def unpack_k_params(k_params: np.ndarray, bits: int = 4, group: int = 128):
     halves = np.ascontiguousarray(k_params).view(np.float16)
     d = k_params.shape[-1]
-    return halves[..., :d].copy(), halves[..., d:].copy()
+    sc, ze = halves[..., :d].copy(), halves[..., d:].copy()
+    slots = param_slots(bits, group)
+    if slots is not None:
+        row, col = slots
+        b, ng, h, _ = sc.shape
+        out = []
+        for t in (sc, ze):
+            src = t.reshape(b, ng // 4, 4, h, d)
+            dst = np.empty_like(src)
+            for g in range(4):
+                dst[:, :, g] = np.moveaxis(src[:, :, row[g], :, col[g]], 0, -1)
+            out.append(dst.reshape(b, ng, h, d))
+        sc, ze = out
+    return sc, ze
 
 
-def pack_v_params(v_scale: np.ndarray, v_zero: np.ndarray) -> np.ndarray:
+def pack_v_params(v_scale: np.ndarray, v_zero: np.ndarray, bits: int = 4, group: int = 128) -> np.ndarray:
     """(b, s, h, d/G) fp16 x2 -> (b, d/G, h, s) float32-typed storage."""
     b, s, h, ng = v_scale.shape
     if s % 128:
@@ -212,12 +262,26 @@ def pack_v_params(v_scale: np.ndarray, v_zero: np.ndarray) -> np.ndarray:
     sc = v_scale.transpose(0, 3, 2, 1).reshape(b, ng, h, s // 128, 1, 128)
     ze = v_zero.transpose(0, 3, 2, 1).reshape(b, ng, h, s // 128, 1, 128)
     both = np.concatenate([sc, ze], axis=4).astype(np.float16)              # (b, ng, h, s/128, 2, 128)
+    slots = param_slots(bits, group)
+    if slots is not None:
+        row, col = slots
+        dst = np.empty_like(both)
+        for g in range(4):
+            dst[:, row[g], :, :, :, col[g]] = np.moveaxis(both[:, g], -1, 0)
+        both = dst
     return np.ascontiguousarray(both.reshape(b, ng, h, 2 * s)).view(np.float32)
 
 
-def unpack_v_params(v_params: np.ndarray):
+def unpack_v_params(v_params: np.ndarray, bits: int = 4, group: int = 128):
     b, ng, h, s = v_params.shape
     halves = np.ascontiguousarray(v_params).view(np.float16).reshape(b, ng, h, s // 128, 2, 128)
+    slots = param_slots(bits, group)
+    if slots is not None:
+        row, col = slots
+        dst = np.empty_like(halves)
+        for g in range(4):
+            dst[:, g] = np.moveaxis(halves[:, row[g], :, :, :, col[g]], 0, -1)
+        halves = dst
     sc = halves[:, :, :, :, 0].reshape(b, ng, h, s).transpose(0, 3, 2, 1)
     ze = halves[:, :, :, :, 1].reshape(b, ng, h, s).transpose(0, 3, 2, 1)
     return np.ascontiguousarray(sc), np.ascontiguousarray(ze)
@@ -229,9 +293,9 @@ def quantize_pack(k, v, bits: int, group: int, dtype: str = "fp16"):
     q = quantize_kv(to_f32(k, dtype), to_f32(v, dtype), bits, group)
     return dict(
         k_pack=pack_k(q["k_codes"], bits),
-        k_params=pack_k_params(q["k_scale"], q["k_zero"]),
+        k_params=pack_k_params(q["k_scale"], q["k_zero"], bits, group),
         v_pack=pack_v(q["v_codes"], bits),
-        v_params=pack_v_params(q["v_scale"], q["v_zero"]),
+        v_params=pack_v_params(q["v_scale"], q["v_zero"], bits, group),
         logical=q,
     )
 
@@ -327,8 +391,8 @@ def decode_from_packed(q, k_pack, k_params, v_pack, v_params, softmax_scale, bit
     decode entry point must match).  q is (b, 1, h, d) or (b, h, d)."""
     kc = unpack_k(k_pack, bits)
     vc = unpack_v(v_pack, bits)
-    ks, kz = unpack_k_params(k_params)
-    vs, vz = unpack_v_params(v_params)
+    ks, kz = unpack_k_params(k_params, bits, group)
+    vs, vz = unpack_v_params(v_params, bits, group)
     logical = dict(k_codes=kc, k_scale=ks, k_zero=kz, v_codes=vc, v_scale=vs, v_zero=vz)
     kd, vd = dequantize(logical, group, out_dtype=dtype)
     qf = to_f32(q, dtype)

@@ -101,3 +101,46 @@ def golden_torch(case, name, device="cpu"):
         return None
     tdt = torch.float16 if case["cfg"]["dtype"] == "fp16" else torch.bfloat16
     return torch.from_numpy(case[name].view(np.int16).copy()).view(tdt).to(device)
+
+
+# ---------------------------------------------------------------------------
+# golden vectors written by the reference's own CUDA kernels (tests/golden/ref_i4.npz, made on a
+# B200 by tests/golden/make_ref_golden.py from the modules oracle/build_ref.py builds)
+# ---------------------------------------------------------------------------
+REF_GOLDEN_PATH = _os.path.join(_os.path.dirname(_os.path.abspath(__file__)), "golden", "ref_i4.npz")
+REF_STORED = ("gqa_g128", "mha_g128", "gqa_g32")            # inputs and packed buffers stored
+REF_HASHED = ("eval_g128", "llama_g128", "llama_g32")       # inputs regenerated from the seed, buffers as SHA-256
+
+
+def _ref_generator():
+    import importlib.util
+    path = _os.path.join(_os.path.dirname(GOLDEN_PATH), "make_ref_golden.py")
+    spec = importlib.util.spec_from_file_location("make_ref_golden", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def load_ref_case(name):
+    """One case of the reference-kernel fixtures: dict(cfg, q, k, v as torch fp16 CPU tensors, blob, sha).
+    Inputs of the hashed cases are regenerated with the generator script's own function and checked
+    against the recorded hashes (None is returned for q/k/v if this torch build draws other numbers)."""
+    gen = _ref_generator()
+    blob = np.load(REF_GOLDEN_PATH)
+    b, s, h, h_k, group, seed, store, crafted = (int(x) for x in blob[f"{name}/meta"])
+    cfg = dict(b=b, s=s, h=h, h_k=h_k, group=group, bits=4, crafted=bool(crafted))
+    if store:
+        q, k, v = (torch.from_numpy(blob[f"{name}/{n}"].view(np.int16).copy()).view(torch.float16) for n in "qkv")
+    else:
+        q, k, v = gen.make_inputs(b, s, h, h_k, seed, bool(crafted))
+        got = np.concatenate([gen.sha(t.numpy().view(np.uint16)) for t in (q, k, v)])
+        if not np.array_equal(got, blob[f"{name}/in_sha"]):
+            q = k = v = None
+    return dict(cfg=cfg, q=q, k=k, v=v, blob=blob, sha=gen.sha, name=name)
+
+
+def params_equal(a_u16: np.ndarray, b_u16: np.ndarray) -> bool:
+    """fp16 scale/zero bit patterns equal, +0.0 and -0.0 taken as the same value (the sign of a
+    zero group minimum depends on the order the reference's reduction meets +0.0 and -0.0)."""
+    a, b = a_u16.ravel(), b_u16.ravel()
+    return bool(np.all((a == b) | (((a | b) & 0x7FFF) == 0)))
