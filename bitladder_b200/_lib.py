@@ -14,12 +14,16 @@ LIB_PATH = os.environ.get("BITDECODE_LIB") or os.path.join(_HERE, "libbitdecode.
 BD_OK = 0
 BD_FP16, BD_BF16, BD_FP32 = 0, 1, 2
 BD_MAX_PARTS = 16
+BD_PACK_APPROX_DIV = 1
+BD_ERR_INVALID, BD_ERR_TIMEOUT, BD_ERR_SCRATCH_LIMIT, BD_ERR_PAGE = -1, -7, -8, -9
 
 EXPORTS = (
     "bd_pack", "bd_decode", "bd_decode_workspace_bytes", "bd_plan_splits",
     "bd_combine", "bd_read_status", "bd_strerror", "bd_version",
     "bd_partition_segments", "bd_partition_parts",
     "bd_decode_noalloc", "bd_noalloc_scratch_bytes",
+    "bd_exchange_area_bytes", "bd_peer_alloc", "bd_peer_free", "bd_peer_export", "bd_peer_open", "bd_peer_close",
+    "bd_exchange_combine", "bd_exchange_put", "bd_exchange_state",
 )
 
 
@@ -34,6 +38,7 @@ class PackArgs(C.Structure):
         ("b", C.c_int32), ("s", C.c_int32), ("h_k", C.c_int32), ("d", C.c_int32),
         ("dst_token_offset", C.c_int32),
         ("bits", C.c_int32), ("group", C.c_int32), ("dtype", C.c_int32),
+        ("flags", C.c_int32),
     ]
 
 
@@ -59,6 +64,7 @@ class DecodeArgs(C.Structure):
         ("k_new", C.c_void_p), ("v_new", C.c_void_p), ("new_stride_b", C.c_int64), ("new_stride_h", C.c_int64),
         ("block_table", C.c_void_p), ("block_table_stride", C.c_int32), ("num_pages", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("spin_limit", C.c_uint32), ("test_starve", C.c_int32),
     ]
 
 
@@ -72,6 +78,18 @@ class CombineArgs(C.Structure):
         ("out", C.c_void_p),
         ("lse", C.c_void_p),
         ("out_dtype", C.c_int32),
+    ]
+
+
+class ExchangeArgs(C.Structure):
+    _fields_ = [
+        ("rank", C.c_int32), ("world", C.c_int32),
+        ("areas", C.POINTER(C.c_void_p)),
+        ("part_out", C.c_void_p), ("part_lse", C.c_void_p),
+        ("rows", C.c_int64),
+        ("d", C.c_int32),
+        ("out", C.c_void_p), ("lse", C.c_void_p),
+        ("out_dtype", C.c_int32), ("spin_limit", C.c_uint32),
     ]
 
 
@@ -111,6 +129,19 @@ def load():
     lib.bd_partition_parts.restype = C.c_int
     lib.bd_read_status.argtypes = [C.c_void_p, C.c_void_p]
     lib.bd_read_status.restype = C.c_int
+    lib.bd_exchange_area_bytes.argtypes = [C.c_int, C.c_int64]
+    lib.bd_exchange_area_bytes.restype = C.c_size_t
+    lib.bd_peer_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p)]
+    lib.bd_peer_free.argtypes = [C.c_void_p]
+    lib.bd_peer_export.argtypes = [C.c_void_p, C.c_void_p]
+    lib.bd_peer_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+    lib.bd_peer_close.argtypes = [C.c_void_p]
+    lib.bd_exchange_combine.argtypes = [C.POINTER(ExchangeArgs), C.c_void_p]
+    lib.bd_exchange_put.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.bd_exchange_state.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32)]
+    for name in ("bd_peer_alloc", "bd_peer_free", "bd_peer_export", "bd_peer_open", "bd_peer_close",
+                 "bd_exchange_combine", "bd_exchange_put", "bd_exchange_state"):
+        getattr(lib, name).restype = C.c_int
     lib.bd_strerror.argtypes = [C.c_int]
     lib.bd_strerror.restype = C.c_char_p
     lib.bd_version.restype = C.c_int

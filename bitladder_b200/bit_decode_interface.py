@@ -14,7 +14,7 @@ Differences from the reference, all of them additions or stricter checks:
   (``k_res``/``v_res``/``res_lens``), per-sequence lengths (``cache_seqlens``),
   a returned log-sum-exp, a caller-provided output / workspace, fp32 output;
 * bf16 inputs and group size 64 are implemented (the reference accepts the
-  arguments but has no kernels for them);
+  arguments but has no kernels for them); group size 32 as in the reference;
 * unsupported ``(quant_mode, group_size, num_bits, dtype)`` combinations raise
   instead of silently doing nothing (reference: ``csrc/bit_decode/decode_api.cpp:207-226``);
 * paged caches (``opt_block_table``): the four packed buffers then hold pages of 256-token
@@ -69,7 +69,7 @@ def _check_cuda(*tensors) -> None:
 def _check_config(quant_mode: str, group_size: int, num_bits: int) -> None:
     _require(quant_mode == "k-channel", f"quant_mode {quant_mode!r} is not supported (only 'k-channel')")
     _require(num_bits in (2, 4), f"num_bits must be 2 or 4, got {num_bits}")
-    _require(group_size in (64, 128), f"group_size must be 64 or 128, got {group_size}")
+    _require(group_size in (32, 64, 128), f"group_size must be 32, 64 or 128, got {group_size}")
 
 
 def _rows_contiguous(t: torch.Tensor) -> bool:
@@ -128,7 +128,7 @@ def kvcache_pack_int(k_cache: torch.Tensor, k_pack: torch.Tensor, k_params: torc
                      quant_mode: str = "k-channel",
                      group_size: int = 128,
                      num_bits: int = 4,
-                     *, dst_token_offset: int = 0) -> None:
+                     *, dst_token_offset: int = 0, reference_fast_math: bool = False) -> None:
     """Quantize ``k_cache``/``v_cache`` (b, s, h_k, d) and pack them in place into
     ``k_pack``/``k_params``/``v_pack``/``v_params``.
 
@@ -136,7 +136,11 @@ def kvcache_pack_int(k_cache: torch.Tensor, k_pack: torch.Tensor, k_params: torc
     there, ``seqlen_k`` is taken from ``k_cache.shape[1]`` and ``cu_seqlens_k`` is
     accepted but not read.  ``dst_token_offset`` (extension) writes the packed
     tokens at that offset of the pack buffers, for caches that grow block by block.
-    Asynchronous on the current stream.
+    ``reference_fast_math`` (extension) divides the way the reference does as it is shipped
+    (built with ``--use_fast_math``: the GPU's approximate reciprocal), which gives the very bytes
+    that build writes on the same GPU; the default is IEEE division, the bytes of the reference
+    built without that flag and of a CPU evaluation of its formulas.  The two differ by one code
+    step at exact rounding ties, a few codes in 10^5.  Asynchronous on the current stream.
     """
     _check_config(quant_mode, group_size, num_bits)
     # A paged pool is packed page by page: quantization groups never cross a pack block, so the
@@ -168,14 +172,15 @@ def kvcache_pack_int(k_cache: torch.Tensor, k_pack: torch.Tensor, k_params: torc
         v_params_stride_b=v_params.stride(0), v_params_stride_g=v_params.stride(1),
         v_params_stride_h=v_params.stride(2),
         b=b, s=s, h_k=h_k, d=d, dst_token_offset=dst_token_offset,
-        bits=num_bits, group=group_size, dtype=_dtype_code(k_cache.dtype))
+        bits=num_bits, group=group_size, dtype=_dtype_code(k_cache.dtype),
+        flags=_lib.BD_PACK_APPROX_DIV if reference_fast_math else 0)
     with torch.cuda.device(k_cache.device):
         _lib.check(_lib.load().bd_pack(C.byref(a), _stream(k_cache.device)), "bd_pack")
 
 
 def _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
                  k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, lse, num_splits, block_table=None,
-                 k_new=None, v_new=None):
+                 k_new=None, v_new=None, spin_limit=0, test_starve=0):
     b, s_cap, h_k, d = _check_packed(k_pack, k_params, v_pack, v_params, num_bits, group_size)
     _require(q.dim() == 4 and q.shape[1] == 1, "q must be (b, 1, h, d): one query token per sequence")
     num_pages = 0
@@ -241,6 +246,7 @@ def _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_siz
     a.dtype, a.out_dtype = _dtype_code(q.dtype), _dtype_code(out.dtype)
     a.softmax_scale = float(softmax_scale)
     a.num_splits = int(num_splits)
+    a.spin_limit, a.test_starve = int(spin_limit), int(test_starve)
     return a
 
 
@@ -283,7 +289,8 @@ def fwd_kvcache_int(q: torch.Tensor,
                     seqlen_k: Optional[int] = None, return_lse: bool = False,
                     out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
                     workspace: Optional[torch.Tensor] = None, num_splits: int = 0,
-                    k_new: Optional[torch.Tensor] = None, v_new: Optional[torch.Tensor] = None):
+                    k_new: Optional[torch.Tensor] = None, v_new: Optional[torch.Tensor] = None,
+                    check: bool = False, spin_limit: int = 0, _test_starve: int = 0):
     """One decode-attention step over the packed cache; returns ``out`` (b, 1, h, d).
 
     Same positional signature as the reference (``bit_decode_interface.py:43-86``),
@@ -300,7 +307,11 @@ def fwd_kvcache_int(q: torch.Tensor,
     with changes); ``k_new``/``v_new`` (b, 1, h_k, d): the K/V rows of the token decoded in this
     step — the step attends over them as the next tail row and stores them at row ``res_lens[b]`` of
     ``k_res``/``v_res`` (fused append; the caller then adds one to ``res_lens``, which must be below
-    the tail buffers' length).  Asynchronous on the current stream.
+    the tail buffers' length).  Asynchronous on the current stream, unless ``check=True``: then the
+    call waits for the step and raises ``RuntimeError`` if the kernel reported an error (a device-side
+    wait on a copy that ran out after ``spin_limit`` polls, 0 = the library's default of seconds; a
+    ``opt_block_table`` entry outside the page pool).  Without ``check`` such a step returns
+    unusable values silently; a serving loop checks every n-th step.
     """
     _check_config(quant_mode, group_size, num_bits)
     _check_cuda(q, k_pack, k_params, v_pack, v_params, k_res, v_res, res_lens, cache_seqlens, out, workspace,
@@ -313,12 +324,22 @@ def fwd_kvcache_int(q: torch.Tensor,
     lse = torch.empty((q.shape[0], q.shape[2]), dtype=torch.float32, device=q.device) if return_lse else None
     a = _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
                      k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, lse, num_splits, opt_block_table,
-                     k_new, v_new)
+                     k_new, v_new, spin_limit, _test_starve)
     with torch.cuda.device(q.device):
         ws = _workspace_for(a, q.device, workspace)
         _lib.check(_lib.load().bd_decode(C.byref(a), _stream(q.device)), "bd_decode")
+        if check:
+            _check_status(ws, q.device)
     del ws
     return (out, lse) if return_lse else out
+
+
+def _check_status(workspace: torch.Tensor, device) -> None:
+    """Wait for the stream and raise if a decode kernel left an error in the workspace's status word."""
+    rc = int(_lib.load().bd_read_status(workspace.data_ptr(), _stream(device)))
+    if rc != 0:
+        workspace.zero_()                 # counters may be anywhere after an aborted step
+        raise RuntimeError(f"decode step failed on the device: {_lib.strerror(rc)} (code {rc})")
 
 
 class DecodeStep:
@@ -338,7 +359,7 @@ class DecodeStep:
     def __init__(self, q, k_pack, k_params, v_pack, v_params, opt_block_table=None, softmax_scale=1.0,
                  quant_mode="k-channel", group_size=128, num_bits=4, *, k_res=None, v_res=None, res_lens=None,
                  cache_seqlens=None, seqlen_k=None, return_lse=False, out=None, out_dtype=None, num_splits=0,
-                 k_new=None, v_new=None, lse=None):
+                 k_new=None, v_new=None, lse=None, spin_limit=0, _test_starve=0):
         _check_config(quant_mode, group_size, num_bits)
         _check_cuda(q, k_pack, k_params, v_pack, v_params, k_res, v_res, res_lens, cache_seqlens, out,
                     opt_block_table, k_new, v_new)
@@ -358,7 +379,7 @@ class DecodeStep:
                         if return_lse else None)
         self._args = _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
                                   k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, self.lse, num_splits,
-                                  opt_block_table, k_new, v_new)
+                                  opt_block_table, k_new, v_new, spin_limit, _test_starve)
         self._device = q.device
         with torch.cuda.device(q.device):
             need = int(_lib.load().bd_decode_workspace_bytes(C.byref(self._args)))
@@ -370,9 +391,11 @@ class DecodeStep:
         self._fn = _lib.load().bd_decode
         self._ref = C.byref(self._args)
 
-    def step(self):
+    def step(self, check: bool = False):
         """Launch the step on the current stream of the tensors' device; returns ``out`` (or
-        ``(out, lse)``), the same buffers every time."""
+        ``(out, lse)``), the same buffers every time.  ``check=True`` waits for the step and raises
+        ``RuntimeError`` if the kernel reported an error (see ``fwd_kvcache_int``); it synchronises,
+        so a loop uses it every n-th step, and never inside a stream capture."""
         if torch.cuda.current_device() != self._device.index:
             with torch.cuda.device(self._device):
                 rc = self._fn(self._ref, _stream(self._device))
@@ -380,7 +403,15 @@ class DecodeStep:
             rc = self._fn(self._ref, _stream(self._device))
         if rc != 0:
             _lib.check(rc, "bd_decode")
+        if check:
+            with torch.cuda.device(self._device):
+                _check_status(self._workspace, self._device)
         return (self.out, self.lse) if self.lse is not None else self.out
+
+    def status(self) -> int:
+        """Wait for the stream; return (and clear) the error code the steps so far left: 0 for none."""
+        with torch.cuda.device(self._device):
+            return int(_lib.load().bd_read_status(self._workspace.data_ptr(), _stream(self._device)))
 
 
 def decode_workspace_bytes(q, k_pack, k_params, v_pack, v_params, group_size=128, num_bits=4,

@@ -85,7 +85,7 @@ int make_map_2d(CUtensorMap *map, const void *base, uint64_t row_words, uint64_t
 int pack_block_tokens(int bits) { return 32 * (16 / bits); }
 
 bool config_supported(int bits, int group, int d) {
-    return (bits == 2 || bits == 4) && (group == 64 || group == 128) && d == 128;
+    return (bits == 2 || bits == 4) && (group == 32 || group == 64 || group == 128) && d == 128;
 }
 
 struct DecodePlan {
@@ -263,13 +263,14 @@ const char *bd_strerror(int code) {
     switch (code) {
         case BD_OK: return "ok";
         case BD_ERR_INVALID: return "invalid argument (null pointer, bad size or stride)";
-        case BD_ERR_UNSUPPORTED: return "unsupported configuration (bits must be 2 or 4, group 64 or 128, head_dim 128, "
+        case BD_ERR_UNSUPPORTED: return "unsupported configuration (bits must be 2 or 4, group 32, 64 or 128, head_dim 128, "
                                         "fp16/bf16, at most 16 query heads per KV head, tail of at most 256 tokens)";
         case BD_ERR_ALIGNMENT: return "pointer or stride not aligned (16-byte pointers, strides in whole rows / multiples of 8)";
         case BD_ERR_WORKSPACE: return "workspace missing or too small (see bd_decode_workspace_bytes)";
         case BD_ERR_CUDA: return "a CUDA runtime or driver call failed";
         case BD_ERR_DEVICE: return "device is not compute capability 10.x";
         case BD_ERR_TIMEOUT: return "a bounded wait inside a kernel ran out";
+        case BD_ERR_PAGE: return "a block_table entry lies outside [0, num_pages); its tokens were left out";
         case BD_ERR_SCRATCH_LIMIT: return "this call needs more scratch than the library's fixed area holds "
                                           "(bd_noalloc_scratch_bytes); use bd_decode with a workspace";
         default: return "unknown error";
@@ -313,6 +314,7 @@ int bd_pack(const bd_pack_args *a, bd_stream_t stream) {
     p.v_params_stride_b = a->v_params_stride_b; p.v_params_stride_g = a->v_params_stride_g;
     p.v_params_stride_h = a->v_params_stride_h;
     p.b = a->b; p.s = a->s; p.h_k = a->h_k; p.dst_token_offset = a->dst_token_offset;
+    p.approx_div = (a->flags & BD_PACK_APPROX_DIV) ? 1 : 0;
     cudaError_t err = bd::launch_pack(p, a->bits, a->group, a->dtype, static_cast<cudaStream_t>(stream));
     return err == cudaSuccess ? BD_OK : BD_ERR_CUDA;
 }
@@ -394,6 +396,9 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     p.block_table = a->block_table;
     p.block_table_stride = a->block_table_stride;
     p.blocks_per_page = a->block_table ? a->s_cap / nb : 0;
+    p.num_pages = a->num_pages;
+    p.spin_limit = a->spin_limit ? a->spin_limit : (1u << 22);
+    p.test_starve = a->test_starve;
     p.k_res = a->k_res; p.v_res = a->v_res;
     p.res_stride_b = a->res_stride_b; p.res_stride_s = a->res_stride_s; p.res_stride_h = a->res_stride_h;
     p.res_lens = a->res_lens; p.res_len = a->k_res ? a->res_len : 0;
@@ -483,10 +488,14 @@ int bd_decode_noalloc(const bd_decode_args *a, bd_stream_t stream_) {
     void *scratch = noalloc_scratch_address(&rc);
     if (rc != BD_OK) return rc;
     // The area keeps whatever the previous call left (partials of another shape may sit
-    // where this call's counters go): clear the status word and the arrival counters,
-    // the only bytes that must start at zero.  No allocation: a memset node on the stream.
+    // where this call's counters go): clear the arrival counters, the only bytes that must
+    // start at zero.  The status word in front of them is left as it is, so an error a step
+    // reported stays readable (bd_read_status(NULL, stream) returns and clears it); a freshly
+    // loaded library has it at zero.  No allocation: a memset node on the stream.
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    if (cudaMemsetAsync(scratch, 0, plan.off_table, stream) != cudaSuccess) return BD_ERR_CUDA;
+    if (cudaMemsetAsync(static_cast<unsigned char *>(scratch) + plan.off_counters, 0,
+                        plan.off_table - plan.off_counters, stream) != cudaSuccess)
+        return BD_ERR_CUDA;
     bd_decode_args args = *a;
     args.workspace = scratch;
     args.workspace_bytes = BD_NOALLOC_SCRATCH_BYTES;
@@ -513,10 +522,15 @@ int bd_combine(const bd_combine_args *a, bd_stream_t stream) {
 }
 
 int bd_read_status(const void *workspace, bd_stream_t stream) {
-    if (!workspace) return BD_ERR_INVALID;
+    if (!workspace) {            // the fixed area of bd_decode_noalloc on the current device
+        int rc = BD_OK;
+        workspace = noalloc_scratch_address(&rc);
+        if (rc != BD_OK) return rc;
+    }
     if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) return BD_ERR_CUDA;
     int32_t v = 0;   // the status word is the first word of the workspace
     if (cudaMemcpy(&v, workspace, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return BD_ERR_CUDA;
+    if (v != 0 && cudaMemset(const_cast<void *>(workspace), 0, sizeof(v)) != cudaSuccess) return BD_ERR_CUDA;
     return v;
 }
 

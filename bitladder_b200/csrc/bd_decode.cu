@@ -84,6 +84,7 @@ struct Cfg {
     static constexpr int NGK = NB / GROUP;              // K token groups per block
     static constexpr int FPG = GROUP / 32;              // K fields per token group
     static constexpr int NGD = kHeadDim / GROUP;        // V dim groups
+    static constexpr int NZ = (NGD + 1) / 2;            // accumulators of sum_t p_t * zero_t (two dim groups each)
     static constexpr int FPGV = P / NGD;                // V fields per dim group
     static constexpr int DP = kHeadDim / P;             // 16-bit words per V row
     static constexpr int RUNS = NB / 128;               // 128-token runs per block (V params)
@@ -96,7 +97,8 @@ struct Cfg {
     static constexpr int FIT = (kSmemLimit - 32) / (WARP_BYTES + 4);
     // eight fields per word (2 bits) and two query tiles both need more than the 168 registers
     // twelve warps leave a thread: eight warps (255 registers) measured 3-4 % faster at 2 bits
-    static constexpr int CAP = (NQT == 1 && BITS == 4) ? kMaxWarps : (kMaxWarps < 8 ? kMaxWarps : 8);
+    // (the same holds for group 32, with four parameter sets per block)
+    static constexpr int CAP = (NQT == 1 && BITS == 4 && GROUP >= 64) ? kMaxWarps : (kMaxWarps < 8 ? kMaxWarps : 8);
     static constexpr int WARPS = FIT < CAP ? FIT : CAP;
     static constexpr int THREADS = WARPS * 32;
     static constexpr size_t OFF_PRM = size_t(WARPS) * 2 * CODE_BYTES;
@@ -124,14 +126,16 @@ __device__ __forceinline__ uint32_t aux_word(uint32_t w) {
 // field above it (f_j + 16 f_{j+1}, a whole byte: still an exact fp16 subnormal), the odd
 // field alone (16 f_{j+1}).  The products are linear, so the even field's sum is the
 // difference of the two accumulators, taken once after the last MMA; that saves the
-// shift and one of the masks on the high byte.  kFieldPairs tells the callers.
-template <int BITS, int J>
+// shift and one of the masks on the high byte.  kFieldPairs tells the callers (with one field
+// per quantization group, group 32, the two fields of a byte have different scales and every
+// field is masked out alone).
+template <int BITS, int J, bool PAIRS>
 __device__ __forceinline__ uint32_t field(uint32_t w, uint32_t aux) {
     uint32_t x;
     if constexpr (BITS == 4) {
-        if constexpr (J == 0) x = w & 0x00ff00ffu;
+        if constexpr (J == 0) x = w & (PAIRS ? 0x00ff00ffu : 0x000f000fu);
         else if constexpr (J == 1) x = w & 0x00f000f0u;
-        else if constexpr (J == 2) x = aux;
+        else if constexpr (J == 2) x = PAIRS ? aux : (aux & 0x000f000fu);
         else x = aux & 0x00f000f0u;
     } else {
         constexpr uint32_t m = 0x00030003u << (2 * (J < 5 ? J : J - 5));
@@ -144,7 +148,8 @@ __device__ __forceinline__ uint32_t field(uint32_t w, uint32_t aux) {
 #endif
     return x;
 }
-template <int BITS> constexpr bool kFieldPairs = (BITS == 4);
+// Pairs need both fields of a byte to meet the same scale: two or more fields per group.
+template <int BITS, int GROUP> constexpr bool kFieldPairs = (BITS == 4 && GROUP >= 64);
 // Value of the fp16 lane produced by field<J> divided by the code.
 template <int BITS>
 __host__ __device__ constexpr float field_weight(int j) {
@@ -162,6 +167,23 @@ __host__ __device__ constexpr float field_weight(int j) {
 #endif
 }
 
+// Byte offset, inside a warp's K parameter tile, of the 8 scales of token group gk for channels
+// 32a + 8l .. +7 (the zeros sit 256 bytes on), and inside its V parameter tile of the scales of
+// tokens r0, r0 + 1 (hi = 0) or r0 + 8, r0 + 9 (hi = 1) of dim group gd, r0 even with r0 % 16 < 8.
+// Natural order, except 4-bit with group 32: the reference's fragment order (element c of group g in
+// row 2*(g%2) + (c/8)%2, column 16*(c/16) + 8*(g/2) + c%8; flash_fwd_kernel.h:939-957).
+template <int BITS, int GROUP>
+__device__ __forceinline__ uint32_t kprm_off(int gk, int a, int l) {
+    if constexpr (BITS == 4 && GROUP == 32) return (2 * (gk & 1) + (l & 1)) * 512 + (16 * (2 * a + (l >> 1)) + 8 * (gk >> 1)) * 2;
+    else return gk * 512 + (32 * a + 8 * l) * 2;
+}
+template <int BITS, int GROUP>
+__device__ __forceinline__ uint32_t vprm_off(int gd, int r0, int hi) {
+    constexpr int RUNS = (32 * (16 / BITS)) / 128;
+    if constexpr (BITS == 4 && GROUP == 32) return (2 * (gd & 1) + hi) * 512 + (16 * (r0 >> 4) + 8 * (gd >> 1) + (r0 & 7)) * 2;
+    else return gd * (RUNS * 512) + (r0 >> 7) * 512 + (r0 & 127) * 2 + 16 * hi;
+}
+
 // One online-softmax step for NT score tiles (m16n8 accumulators, columns = query
 // rows).  On entry t holds the scores in log2 units MINUS the running maximum of
 // their column (minus 0 while the column has no maximum yet); on exit it holds
@@ -170,9 +192,9 @@ __host__ __device__ constexpr float field_weight(int j) {
 // are rescaled a handful of times per sequence.  With ACC_L the probabilities are
 // also added to l_run (otherwise the caller gets the row sums elsewhere).
 // Returns true when a rescale happened (f holds the factor per column parity).
-template <int NT, bool ACC_L>
+template <int NT, bool ACC_L, int NZ>
 __device__ __forceinline__ bool softmax_step(float (&t)[NT][4], float (&m_run)[2], float (&l_run)[2],
-                                             float (&O)[8][4], float (&ZS)[4], float (&f)[2]) {
+                                             float (&O)[8][4], float (&ZS)[NZ][4], float (&f)[2]) {
     float cmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int j = 0; j < NT; ++j)
@@ -205,7 +227,9 @@ __device__ __forceinline__ bool softmax_step(float (&t)[NT][4], float (&m_run)[2
 #pragma unroll
             for (int e = 0; e < 4; ++e) O[mt][e] *= f[e & 1];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) ZS[e] *= f[e & 1];
+        for (int z = 0; z < NZ; ++z)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ZS[z][e] *= f[e & 1];
 #pragma unroll
         for (int j = 0; j < NT; ++j)
 #pragma unroll
@@ -258,7 +282,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                  const __grid_constant__ CUtensorMap vmap) {
     using C = Cfg<BITS, GROUP, NQT>;
     constexpr int P = C::P, NB = C::NB, NGK = C::NGK, FPG = C::FPG, NGD = C::NGD, FPGV = C::FPGV;
-    constexpr int DP = C::DP, RUNS = C::RUNS, PRM = C::PRM_BYTES, NACC = C::NACC;
+    constexpr int DP = C::DP, RUNS = C::RUNS, PRM = C::PRM_BYTES, NACC = C::NACC, NZ = C::NZ;
     constexpr int kWarps = C::WARPS;
 
     // The swizzled TMA tiles need a 1024-byte aligned base; dynamic shared memory
@@ -320,7 +344,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
         ib = ok ? page : 0;
         return ok;
     };
-    bool starve = p.test_starve != 0 && blockIdx.x == 0 && warp == 0;     // test hook, first copy only
+    bool starve = p.test_starve != 0 && blockIdx.x == 0;     // test hook: the first K copy of every warp of CTA 0
     auto issue_k = [&](int ib, int blk) {
         resolve(ib, blk);
         mbar_arrive_expect_tx(kbar, C::CODE_BYTES + PRM + (starve ? 16 : 0));
@@ -445,7 +469,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
         }
 
         float O[NQT][8][4];
-        float ZS[NQT][4];
+        float ZS[NQT][NZ][4];
         float m_run[NQT][2], l_run[NQT][2];
 #pragma unroll
         for (int nq = 0; nq < NQT; ++nq) {
@@ -454,7 +478,9 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
                 for (int e = 0; e < 4; ++e) O[nq][mt][e] = 0.f;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) ZS[nq][e] = 0.f;
+            for (int z = 0; z < NZ; ++z)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) ZS[nq][z][e] = 0.f;
             m_run[nq][0] = m_run[nq][1] = -INFINITY;
             l_run[nq][0] = l_run[nq][1] = 0.f;
         }
@@ -526,7 +552,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                     S1[nq][0][e] = ok ? fmaf(S1[nq][0][e], p.scale_log2, -mu) : -INFINITY;
                 }
                 float f[2];
-                softmax_step<1, true>(S1[nq], m_run[nq], l_run[nq], O[nq], ZS[nq], f);
+                softmax_step<1, true, NZ>(S1[nq], m_run[nq], l_run[nq], O[nq], ZS[nq], f);
                 pb[nq][0] = movmatrix_trans(pack_f16x2(S1[nq][0][0], S1[nq][0][1]));
                 pb[nq][1] = movmatrix_trans(pack_f16x2(S1[nq][0][2], S1[nq][0][3]));
             }
@@ -547,7 +573,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         O[nq][mt][e] = fmaf(ot[e], fw, O[nq][mt][e]);
-                        if constexpr (kFieldPairs<BITS>) {          // the accumulator below holds the pair sum
+                        if constexpr (kFieldPairs<BITS, GROUP>) {          // the accumulator below holds the pair sum
                             if (mt & 1) O[nq][mt - 1][e] = fmaf(ot[e], fw, O[nq][mt - 1][e]);
                         }
                     }
@@ -561,7 +587,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                 int pib = ib, pblk = blk;
                 if (!resolve(pib, pblk)) {        // page index outside the pool: the whole block is masked
                     seqlen_blk = blk * NB;
-                    if (lane == 0) atomicExch(p.status, BD_ERR_INVALID);
+                    if (lane == 0) atomicExch(p.status, BD_ERR_PAGE);
                 }
             }
             const bool need_mask = (blk + 1) * NB > seqlen_blk;
@@ -584,7 +610,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
                     for (int a = 0; a < 4; ++a) {
                         uint32_t z0, z1, z2, z3;
-                        lds128(kprm + gk * 512 + 256 + (32 * a + 8 * l) * 2, z0, z1, z2, z3);
+                        lds128(kprm + kprm_off<BITS, GROUP>(gk, a, l) + 256, z0, z1, z2, z3);
 #pragma unroll
                         for (int nq = 0; nq < NQT; ++nq) {
                             mma_f16(Z[gk][nq], z0, z0, z1, z1, qr[nq][a][0], qr[nq][a][1]);
@@ -626,7 +652,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
                     for (int gk = 0; gk < NGK; ++gk) {
                         uint32_t s0, s1, s2, s3;
-                        lds128(kprm + gk * 512 + (32 * a + 8 * l) * 2, s0, s1, s2, s3);
+                        lds128(kprm + kprm_off<BITS, GROUP>(gk, a, l), s0, s1, s2, s3);
 #pragma unroll
                         for (int nq = 0; nq < NQT; ++nq) {
                             qs[gk][nq][0] = hmul2_u32(qr[nq][a][0], s0);
@@ -652,8 +678,8 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                             constexpr int J = decltype(jc)::value;
 #pragma unroll
                             for (int x = 0; x < 4; ++x) {
-                                F[J][2 * x] = field<BITS, J>(wl[x], wls[x]);
-                                F[J][2 * x + 1] = field<BITS, J>(wh[x], whs[x]);
+                                F[J][2 * x] = field<BITS, J, kFieldPairs<BITS, GROUP>>(wl[x], wls[x]);
+                                F[J][2 * x + 1] = field<BITS, J, kFieldPairs<BITS, GROUP>>(wh[x], whs[x]);
                             }
                         };
                         extract(std::integral_constant<int, 0>{});
@@ -694,7 +720,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
                                 float sv = S[uu][j][nq][e];
-                                if constexpr (kFieldPairs<BITS>) {
+                                if constexpr (kFieldPairs<BITS, GROUP>) {
                                     if ((j & 1) == 0) sv -= S[uu][j + 1][nq][e];   // pair sum minus the odd field
                                 }
                                 t[uu * P + j][e] = fmaf(sv, mjs[j], zm[j / FPG][e & 1]);
@@ -711,7 +737,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                                 }
                     }
                     float f[2];
-                    if (softmax_step<UG * P, (NGD > 1)>(t, m_run[nq], l_run[nq], O[nq], ZS[nq], f) && ug > 0) {
+                    if (softmax_step<UG * P, (NGD > 1), NZ>(t, m_run[nq], l_run[nq], O[nq], ZS[nq], f) && ug > 0) {
                         // The earlier units' probabilities are still waiting (as B fragments,
                         // column = g) for the V phase: bring them to the new maximum too.
                         const float f0 = __shfl_sync(0xffffffffu, f[0], g >> 1);
@@ -766,15 +792,14 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                 for (int j = 0; j < P; ++j) {
                     const int T0 = 16 * u + 32 * j;                       // first token of this k-slice
                     const int r0 = T0 + 2 * l;                            // tokens of fragment register 0
-                    const uint32_t pofs = (r0 >> 7) * 512 + (r0 & 127) * 2;   // run, position (r0+8 stays in the run)
-                    uint32_t sc0[NGD], sc1[NGD], ze0[NGD], ze1[NGD];
+                    uint32_t sc0[NGD], sc1[NGD], ze0[NGD], ze1[NGD];    // tokens r0, r0+1 and r0+8, r0+9 (same run)
 #pragma unroll
                     for (int gd = 0; gd < NGD; ++gd) {
-                        const uint32_t b0 = vprm + gd * (RUNS * 512) + pofs;
+                        const uint32_t b0 = vprm + vprm_off<BITS, GROUP>(gd, r0, 0), b1 = vprm + vprm_off<BITS, GROUP>(gd, r0, 1);
                         sc0[gd] = lds32(b0);
-                        sc1[gd] = lds32(b0 + 16);
+                        sc1[gd] = lds32(b1);
                         ze0[gd] = lds32(b0 + 256);
-                        ze1[gd] = lds32(b0 + 256 + 16);
+                        ze1[gd] = lds32(b1 + 256);
                     }
                     if (need_mask) {          // params of tokens past the end may be uninitialised
                         const int tok = blk * NB + r0;
@@ -790,8 +815,10 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                         // group 1 or, with a single dim group, sum_t p_t (the softmax denominator,
                         // from the same rounded probabilities the numerator uses)
                         constexpr uint32_t kOnes = 0x3c003c00u;
-                        mma_f16(ZS[nq], ze0[0], NGD > 1 ? ze0[NGD - 1] : kOnes, ze1[0], NGD > 1 ? ze1[NGD - 1] : kOnes,
-                                pbu[j][nq][0], pbu[j][nq][1]);
+#pragma unroll
+                        for (int z = 0; z < NZ; ++z)
+                            mma_f16(ZS[nq][z], ze0[2 * z], NGD > 1 ? ze0[NGD > 1 ? 2 * z + 1 : 0] : kOnes, ze1[2 * z],
+                                    NGD > 1 ? ze1[NGD > 1 ? 2 * z + 1 : 0] : kOnes, pbu[j][nq][0], pbu[j][nq][1]);
 #pragma unroll
                         for (int gd = 0; gd < NGD; ++gd) {
                             pv[gd][nq][0] = hmul2_u32(pbu[j][nq][0], sc0[gd]);
@@ -810,8 +837,10 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                             const int mt = (BITS == 4) ? (cb * 4 + JV) : JV;
 #pragma unroll
                             for (int nq = 0; nq < NQT; ++nq)
-                                mma_f16(O[nq][mt], field<BITS, JV>(r0w, s0w), field<BITS, JV>(r1w, s1w),
-                                        field<BITS, JV>(r2w, s2w), field<BITS, JV>(r3w, s3w),
+                                mma_f16(O[nq][mt], field<BITS, JV, kFieldPairs<BITS, GROUP>>(r0w, s0w),
+                                        field<BITS, JV, kFieldPairs<BITS, GROUP>>(r1w, s1w),
+                                        field<BITS, JV, kFieldPairs<BITS, GROUP>>(r2w, s2w),
+                                        field<BITS, JV, kFieldPairs<BITS, GROUP>>(r3w, s3w),
                                         pv[gd][nq][0], pv[gd][nq][1]);
                         };
                         do_vfield(std::integral_constant<int, 0>{});
@@ -865,10 +894,10 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     float ov = O[nq][mt][e];
-                    if constexpr (kFieldPairs<BITS>) {
+                    if constexpr (kFieldPairs<BITS, GROUP>) {
                         if ((mt & 1) == 0) ov -= O[nq][mt + 1][e];      // pair sum minus the odd field
                     }
-                    acc[(nq * 8 + mt) * 4 + e] = fmaf(ov, wgt, ZS[nq][(gd == 0 ? 0 : 2) + (e & 1)]);
+                    acc[(nq * 8 + mt) * 4 + e] = fmaf(ov, wgt, ZS[nq][gd >> 1][2 * (gd & 1) + (e & 1)]);
                 }
             }
 #pragma unroll
@@ -877,7 +906,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                 sum += __shfl_xor_sync(0xffffffffu, sum, 4);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 8);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 16);
-                if (NGD == 1) sum += ZS[nq][2 + c];  // every row of the ones block holds the column sum
+                if (NGD == 1) sum += ZS[nq][0][2 + c];  // every row of the ones block holds the column sum
                 acc[32 * NQT + nq * 4 + c] = m_run[nq][c];
                 acc[32 * NQT + nq * 4 + 2 + c] = sum;
             }
@@ -1368,6 +1397,8 @@ cudaError_t launch_decode(const DecodeParams &p, const CUtensorMap &kmap, const 
     if (bits == 4 && group == 64) return launch_bg<4, 64>(p, kmap, vmap, stream);
     if (bits == 2 && group == 128) return launch_bg<2, 128>(p, kmap, vmap, stream);
     if (bits == 2 && group == 64) return launch_bg<2, 64>(p, kmap, vmap, stream);
+    if (bits == 4 && group == 32) return launch_bg<4, 32>(p, kmap, vmap, stream);
+    if (bits == 2 && group == 32) return launch_bg<2, 32>(p, kmap, vmap, stream);
     return cudaErrorInvalidValue;
 }
 
@@ -1381,7 +1412,9 @@ cudaError_t launch_prefix(const PrefixParams &p, cudaStream_t stream) {
     if (bits == 4 && group == 128) return nqt == 1 ? Cfg<4, 128, 1>::FIELD : Cfg<4, 128, 2>::FIELD;     \
     if (bits == 4 && group == 64) return nqt == 1 ? Cfg<4, 64, 1>::FIELD : Cfg<4, 64, 2>::FIELD;        \
     if (bits == 2 && group == 128) return nqt == 1 ? Cfg<2, 128, 1>::FIELD : Cfg<2, 128, 2>::FIELD;     \
-    if (bits == 2 && group == 64) return nqt == 1 ? Cfg<2, 64, 1>::FIELD : Cfg<2, 64, 2>::FIELD;
+    if (bits == 2 && group == 64) return nqt == 1 ? Cfg<2, 64, 1>::FIELD : Cfg<2, 64, 2>::FIELD;        \
+    if (bits == 4 && group == 32) return nqt == 1 ? Cfg<4, 32, 1>::FIELD : Cfg<4, 32, 2>::FIELD;        \
+    if (bits == 2 && group == 32) return nqt == 1 ? Cfg<2, 32, 1>::FIELD : Cfg<2, 32, 2>::FIELD;
 
 // Streaming warps per CTA of the kernel that serves this configuration.
 int decode_warps(int bits, int group, int gq) {
@@ -1400,6 +1433,8 @@ int decode_ctas_per_sm(int bits, int group, int gq) {
     if (bits == 4 && group == 64) return nqt == 1 ? Cfg<4, 64, 1>::CTAS_PER_SM : Cfg<4, 64, 2>::CTAS_PER_SM;
     if (bits == 2 && group == 128) return nqt == 1 ? Cfg<2, 128, 1>::CTAS_PER_SM : Cfg<2, 128, 2>::CTAS_PER_SM;
     if (bits == 2 && group == 64) return nqt == 1 ? Cfg<2, 64, 1>::CTAS_PER_SM : Cfg<2, 64, 2>::CTAS_PER_SM;
+    if (bits == 4 && group == 32) return nqt == 1 ? Cfg<4, 32, 1>::CTAS_PER_SM : Cfg<4, 32, 2>::CTAS_PER_SM;
+    if (bits == 2 && group == 32) return nqt == 1 ? Cfg<2, 32, 1>::CTAS_PER_SM : Cfg<2, 32, 2>::CTAS_PER_SM;
     return 2;
 }
 

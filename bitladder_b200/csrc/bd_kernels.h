@@ -25,6 +25,7 @@ struct PackParams {
     int64_t v_params_stride_b, v_params_stride_g, v_params_stride_h;   // 4-byte slots
     int32_t b, s, h_k;
     int32_t dst_token_offset;
+    int32_t approx_div;           // divide like the reference built with --use_fast_math (see bd_pack.cu)
 };
 
 // ---------------------------------------------------------------------------
@@ -207,7 +208,7 @@ struct DecodeParams {
     int32_t out_dtype;
     int32_t defer_merge;          // the parts of a sequence are merged by bd_merge_parts_kernel, launched next
     uint32_t spin_limit;          // polls a wait on a copy may take before the warp gives up
-    int32_t test_starve;          // test hook: warp 0 of CTA 0 expects 16 bytes more than its first copy brings
+    int32_t test_starve;          // test hook: the warps of CTA 0 expect 16 bytes more than their first copy brings
     int32_t *status;
 };
 

@@ -6,7 +6,9 @@
 // stored scale and zero; :266-281 for subtract, multiply, roundf, clamp; :283-294
 // for the field order inside a word).  Explicit round-to-nearest intrinsics keep
 // the result independent of compiler flags, so codes, scales and zeros are
-// bit-identical to a CPU evaluation of the same formulas.
+// bit-identical to a CPU evaluation of the same formulas, and to what the reference's kernel
+// writes when it is built without --use_fast_math (4-bit, group 128 and 32).  PackParams::approx_div
+// selects the division of the reference as shipped instead (see scale_from_minmax).
 //
 // One CTA handles one pack block (NB = 32 * 16/bits tokens) of one KV head.
 // The work is pure streaming (read 2*NB*d*2 bytes, write a quarter or an eighth
@@ -71,10 +73,37 @@ __device__ __forceinline__ uint32_t put_field(uint32_t acc, uint32_t qbits) {
     else return acc | ((qbits << (BITS * J - 1)) & kMask);
 }
 
-__device__ __forceinline__ void scale_from_minmax(float mn, float mx, float maxv, float &scale_inv, float &scale) {
+// approx_div: divide the way the reference does as it is shipped (built with --use_fast_math,
+// setup.py:149): maxv / range becomes maxv times the GPU's approximate reciprocal, which is one ulp
+// off the IEEE quotient in about a quarter of the groups and so moves a code by one step where
+// (x - mn) * maxv / range is exactly k + 0.5.  Same bytes as that build on the same GPU; not
+// reproducible on a CPU.  Default (0): IEEE division, the bytes the reference writes when built
+// without that flag, and what a CPU evaluation of the formulas gives.
+__device__ __forceinline__ void scale_from_minmax(float mn, float mx, float maxv, bool approx_div, float &scale_inv,
+                                                  float &scale) {
     const float range = __fsub_rn(mx, mn);
-    scale_inv = (range > 0.0f) ? __fdiv_rn(maxv, range) : 0.0f;
-    scale = (scale_inv == 0.0f) ? 0.0f : __fdiv_rn(1.0f, scale_inv);
+    if (approx_div) {
+        scale_inv = (range > 0.0f) ? __fdividef(maxv, range) : 0.0f;
+        scale = (scale_inv == 0.0f) ? 0.0f : __fdividef(1.0f, scale_inv);
+    } else {
+        scale_inv = (range > 0.0f) ? __fdiv_rn(maxv, range) : 0.0f;
+        scale = (scale_inv == 0.0f) ? 0.0f : __fdiv_rn(1.0f, scale_inv);
+    }
+}
+
+// Where the parameters of (group g of the block / 128-token run, element c of 0..127) are stored:
+// natural order, except 4-bit with group 32, where the reference keeps the order of its MMA
+// fragments (csrc/bit_decode/src/flash_fwd_kernel.h:939-957 with num_params = 4): row
+// 2*(g%2) + (c/8)%2, fp16 column 16*(c/16) + 8*(g/2) + c%8.  Pairs (c even, c + 1) stay adjacent.
+template <int BITS, int GROUP>
+__device__ __forceinline__ void param_slot(int g, int c, int &row, int &col) {
+    if constexpr (BITS == 4 && GROUP == 32) {
+        row = 2 * (g & 1) + ((c >> 3) & 1);
+        col = 16 * (c >> 4) + 8 * (g >> 1) + (c & 7);
+    } else {
+        row = g;
+        col = c;
+    }
 }
 
 // Four token subsets of 64 threads per CTA; resident threads per SM (and with them the
@@ -97,6 +126,7 @@ bd_pack_kernel(const PackParams p) {
     constexpr int NGD = D / GROUP;          // V dim groups
     constexpr int FPGV = P / NGD;           // V fields per dim group
     const float maxv = static_cast<float>((1 << BITS) - 1);
+    const bool approx_div = p.approx_div != 0;
 
     __shared__ float red[NT][NGK][2][D];
     __shared__ __half vprm[NGD][2][NB];
@@ -159,17 +189,19 @@ bd_pack_kernel(const PackParams p) {
                 }
                 mn[gk][e] = a;
                 float sc;
-                scale_from_minmax(a, b, maxv, sinv[gk][e], sc);
+                scale_from_minmax(a, b, maxv, approx_div, sinv[gk][e], sc);
                 mx[gk][e] = sc;   // reuse as the stored scale
             }
         if (T == 0) {
 #pragma unroll
             for (int gk = 0; gk < NGK; ++gk) {
-                const int64_t grow = static_cast<int64_t>(dst_blk) * NGK + gk;
+                int prow, pcol;
+                param_slot<BITS, GROUP>(gk, 2 * cp, prow, pcol);
+                const int64_t grow = static_cast<int64_t>(dst_blk) * NGK + prow;
                 __half *prm = reinterpret_cast<__half *>(p.k_params) +
                               2 * (ib * p.k_params_stride_b + (grow * p.h_k + ih) * D);
-                *reinterpret_cast<__half2 *>(prm + 2 * cp) = __floats2half2_rn(mx[gk][0], mx[gk][1]);
-                *reinterpret_cast<__half2 *>(prm + D + 2 * cp) = __floats2half2_rn(mn[gk][0], mn[gk][1]);
+                *reinterpret_cast<__half2 *>(prm + pcol) = __floats2half2_rn(mx[gk][0], mx[gk][1]);
+                *reinterpret_cast<__half2 *>(prm + D + pcol) = __floats2half2_rn(mn[gk][0], mn[gk][1]);
             }
         }
         uint16_t *kp = static_cast<uint16_t *>(p.k_pack) + ib * p.k_pack_stride_b +
@@ -250,7 +282,7 @@ bd_pack_kernel(const PackParams p) {
                     mx[gd] = fmaxf(mx[gd], __shfl_xor_sync(0xffffffffu, mx[gd], off));
                 }
                 float sc;
-                scale_from_minmax(mn[gd], mx[gd], maxv, sinv[gd], sc);
+                scale_from_minmax(mn[gd], mx[gd], maxv, approx_div, sinv[gd], sc);
                 if (q8 == 0) {
                     vprm[gd][0][t] = __float2half_rn(sc);
                     vprm[gd][1][t] = __float2half_rn(mn[gd]);
@@ -288,9 +320,11 @@ bd_pack_kernel(const PackParams p) {
             const int z = (i >> 6) & 1;            // 0 scales, 1 zeros
             const int run = (i >> 7) % RUNS;
             const int gd = (i >> 7) / RUNS;
+            int plane, pcol;
+            param_slot<BITS, GROUP>(gd, 2 * w, plane, pcol);
             __half *dst = reinterpret_cast<__half *>(p.v_params) +
-                          2 * (ib * p.v_params_stride_b + gd * p.v_params_stride_g + ih * p.v_params_stride_h) +
-                          256 * (run0 + run) + 128 * z + 2 * w;
+                          2 * (ib * p.v_params_stride_b + plane * p.v_params_stride_g + ih * p.v_params_stride_h) +
+                          256 * (run0 + run) + 128 * z + pcol;
             *reinterpret_cast<__half2 *>(dst) = *reinterpret_cast<const __half2 *>(&vprm[gd][z][128 * run + 2 * w]);
         }
     }
@@ -311,6 +345,8 @@ cudaError_t launch_pack(const PackParams &p, int bits, int group, int dtype, cud
     if (bits == 4 && group == 64)  return bf ? launch_pack_t<4, 64, true>(p, stream)  : launch_pack_t<4, 64, false>(p, stream);
     if (bits == 2 && group == 128) return bf ? launch_pack_t<2, 128, true>(p, stream) : launch_pack_t<2, 128, false>(p, stream);
     if (bits == 2 && group == 64)  return bf ? launch_pack_t<2, 64, true>(p, stream)  : launch_pack_t<2, 64, false>(p, stream);
+    if (bits == 4 && group == 32)  return bf ? launch_pack_t<4, 32, true>(p, stream)  : launch_pack_t<4, 32, false>(p, stream);
+    if (bits == 2 && group == 32)  return bf ? launch_pack_t<2, 32, true>(p, stream)  : launch_pack_t<2, 32, false>(p, stream);
     return cudaErrorInvalidValue;
 }
 

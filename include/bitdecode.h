@@ -22,9 +22,13 @@
  *   v_params (b, d/G, h_k, s)   f32-sized slots holding 2*s fp16: per run of 128 tokens,
  *                                     128 scales then 128 zeros
  *
- * For bits = 4, G = 128 these are byte-identical to what the reference's
- * kernels write (reference: csrc/bit_decode/src/include/qpack.h:283-294 and
- * csrc/bit_decode/src/flash_fwd_kernel.h:939-957).
+ * For bits = 4 with G = 128 and G = 32 these are the reference's own layouts (reference:
+ * csrc/bit_decode/src/include/qpack.h:283-294 and csrc/bit_decode/src/flash_fwd_kernel.h:939-957),
+ * checked byte for byte against what its kernels write on a B200 (tests/golden/ref_i4.npz).  With
+ * bits = 4, G = 32 the reference keeps the parameters in the order of its MMA fragments: the scale of
+ * (group g of a pack block / 128-token run, element c) sits in parameter row 2*(g%2) + (c/8)%2 at
+ * fp16 column 16*(c/16) + 8*(g/2) + c%8.  The 2-bit layouts and G = 64 are defined by this library
+ * (natural order): the reference's 2-bit V packer is not usable and it has no G = 64 kernels.
  */
 #ifndef BITDECODE_H_
 #define BITDECODE_H_
@@ -36,7 +40,7 @@
 extern "C" {
 #endif
 
-#define BD_VERSION 100
+#define BD_VERSION 200
 
 /* status codes */
 #define BD_OK                0
@@ -47,6 +51,8 @@ extern "C" {
 #define BD_ERR_CUDA         -5   /* a CUDA runtime / driver call failed */
 #define BD_ERR_DEVICE       -6   /* not an sm_100 device */
 #define BD_ERR_TIMEOUT      -7   /* a bounded device-side wait ran out (see bd_read_status) */
+#define BD_ERR_PAGE         -9   /* status word: a block_table entry outside [0, num_pages) was met; its
+                                    tokens were left out */
 #define BD_ERR_SCRATCH_LIMIT -8  /* bd_decode_noalloc: the call needs more than the fixed scratch area */
 
 /* element types */
@@ -82,9 +88,20 @@ typedef struct bd_pack_args {
     int32_t b, s, h_k, d;
     int32_t dst_token_offset;
     int32_t bits;             /* 2 or 4 */
-    int32_t group;            /* 64 or 128 */
+    int32_t group;            /* 32, 64 or 128 */
     int32_t dtype;            /* BD_FP16 or BD_BF16 */
+    int32_t flags;            /* 0, or BD_PACK_APPROX_DIV */
 } bd_pack_args;
+
+/*
+ * How max_code / range is divided.  Default: IEEE division; the packed bytes equal what the
+ * reference's kernel writes when built without --use_fast_math and what a CPU evaluation of
+ * its formulas gives.  BD_PACK_APPROX_DIV: the GPU's approximate reciprocal, as in the reference
+ * the way it is shipped (--use_fast_math, setup.py:149); byte-identical to that build on the
+ * same GPU.  The two differ by one code step where (x - min) * max_code / range is exactly
+ * k + 0.5, a few codes in 10^5.
+ */
+#define BD_PACK_APPROX_DIV 1
 
 int bd_pack(const bd_pack_args *args, bd_stream_t stream);
 
@@ -153,6 +170,11 @@ typedef struct bd_decode_args {
     int32_t num_pages;
     void *workspace;
     size_t workspace_bytes;
+    uint32_t spin_limit;      /* polls a device-side wait on a copy may take before it gives up with
+                                 BD_ERR_TIMEOUT; 0 = the default (about 2^22, seconds) */
+    int32_t test_starve;      /* test hook, leave 0.  1: the warps of the first CTA expect 16 bytes more
+                                 than their first copy delivers, so their bounded waits run out (nothing
+                                 faults or hangs: the kernel sets BD_ERR_TIMEOUT and returns) */
 } bd_decode_args;
 
 int bd_decode(const bd_decode_args *args, bd_stream_t stream);
@@ -176,8 +198,9 @@ size_t bd_decode_workspace_bytes(const bd_decode_args *args);
  * bytes until the process exits, whether this entry point is used or not.
  *
  *  - It calls no cudaMalloc / cudaFree and no allocating library routine; per
- *    call it queues one small memset (status word and counters) and the decode
- *    kernel(s) on `stream`.
+ *    call it queues one small memset (the arrival counters) and the decode
+ *    kernel(s) on `stream`.  The status word is left alone, so an error code a
+ *    step wrote stays until bd_read_status(NULL, stream) fetches and clears it.
  *  - The first call on each device looks up the area's device address (with
  *    that device current).  Make that first call outside any stream capture.
  *  - A call whose shapes need more than BD_NOALLOC_SCRATCH_BYTES (large batch *
@@ -245,10 +268,62 @@ typedef struct bd_combine_args {
 int bd_combine(const bd_combine_args *args, bd_stream_t stream);
 
 /*
- * Blocks until the work queued on `stream` is done and returns the status word
- * the last bd_decode on that workspace left: BD_OK, or BD_ERR_TIMEOUT if a
- * bounded wait inside a kernel ran out.  Synchronises; meant for tests and
- * debugging, not for the hot path.
+ * Sequence split over GPUs: exchange of the per-GPU partial results and their merge in ONE kernel per
+ * rank and step, over peer-mapped memory (no counterpart in the reference, which is single-GPU; the
+ * merge is its split combine applied across GPUs).  One process per GPU.
+ *
+ * Set-up (allocates; never on the step): every rank allocates an exchange area of
+ * bd_exchange_area_bytes(world, rows) with bd_peer_alloc (zero-filled device memory that can be
+ * shared), exports it with bd_peer_export (a 64-byte handle to pass to the other processes by any
+ * host-side means) and maps the others' with bd_peer_open.  rows = batch * query heads.
+ *
+ * Step: after the local decode has written this rank's normalised partial (part_out fp32 (rows, 128),
+ * part_lse (rows); bd_decode with out_dtype = BD_FP32 and lse), bd_exchange_combine stores the partial
+ * into every peer's area with plain 16-byte stores and sets a per-rank flag there, waits (bounded) for
+ * the flags of all peers in its own area, merges the `world` partials and writes `out` (and `lse`): the
+ * full result on every rank.  It allocates nothing, synchronises nothing on the host and can be
+ * captured in a CUDA graph: the step counter ("epoch") lives in the area.  All ranks must call it the
+ * same number of times; the areas hold two steps, so ranks may be up to one step apart.
+ *
+ * A rank whose peer does not publish within `spin_limit` polls (0 = the default, seconds) does not
+ * write `out`; its kernel puts BD_ERR_TIMEOUT into the area's status word and returns normally.
+ * bd_exchange_state waits for `stream`, returns that word (and clears it) and the area's epoch.
+ * After a timeout the ranks are out of step: zero all areas (with the ranks quiesced) before going on.
+ *
+ * bd_exchange_put publishes a partial into an area from the HOST side (copies + flag), standing in for
+ * a peer's kernel: for tests on one GPU and for partials that arrive by other means.  Synchronises.
+ */
+typedef struct bd_exchange_args {
+    int32_t rank, world;                  /* world <= BD_MAX_PARTS */
+    void *const *areas;                   /* host array of `world` device pointers: rank r's area as mapped
+                                             into this process; areas[rank] is this rank's own */
+    const float *part_out;                /* (rows, d) fp32, normalised within this rank's tokens */
+    const float *part_lse;                /* (rows) */
+    int64_t rows;                         /* b * h */
+    int32_t d;                            /* 128 */
+    void *out;                            /* (rows, d) in out_dtype */
+    float *lse;                           /* optional (rows) */
+    int32_t out_dtype;
+    uint32_t spin_limit;
+} bd_exchange_args;
+
+size_t bd_exchange_area_bytes(int world, int64_t rows);
+int bd_peer_alloc(size_t bytes, void **ptr);
+int bd_peer_free(void *ptr);
+int bd_peer_export(const void *ptr, void *handle64);
+int bd_peer_open(const void *handle64, void **ptr);
+int bd_peer_close(void *ptr);
+int bd_exchange_combine(const bd_exchange_args *args, bd_stream_t stream);
+int bd_exchange_put(void *area, int world, int64_t rows, int from_rank, uint32_t epoch, const float *part_out,
+                    const float *part_lse, bd_stream_t stream);
+int bd_exchange_state(const void *area, bd_stream_t stream, uint32_t *epoch_out);
+
+/*
+ * Blocks until the work queued on `stream` is done, returns the status word the decode calls on
+ * that workspace left (BD_OK, BD_ERR_TIMEOUT if a bounded wait inside a kernel ran out,
+ * BD_ERR_PAGE for a bad block_table entry) and sets the word back to zero.  workspace == NULL
+ * reads the fixed area bd_decode_noalloc uses on the current device.  Synchronises: for tests,
+ * debugging and callers that check every n-th step, not for the hot path.
  */
 int bd_read_status(const void *workspace, bd_stream_t stream);
 

@@ -151,6 +151,48 @@ def load(variant: str = "fast", relaxed: bool = True):
     return mod
 
 
+def time_decode_c2(variant: str = "fast", steps: int = 200) -> float:
+    """Microseconds per step of the reference's split-KV decode (+ combine) kernels on the headline shape
+    (batch 8, 32 query / 8 KV heads, 32768 tokens, 4-bit, group 128; no tail: the reference has none),
+    CUDA-event timed over three rotating caches packed by the reference's own pack kernel.  Launched
+    eagerly through the reference's host API, which allocates its split buffers on every call."""
+    import math
+    import torch
+    mod_pack, mod_decode = load(variant, relaxed=False), load(variant, relaxed=True)
+    b, s, h, h_k, dev = 8, 32768, 32, 8, "cuda"
+    g = torch.Generator(device=dev).manual_seed(7)
+    caches = []
+    for _ in range(3):
+        k_pack = torch.zeros((b, s // 4, h_k, 128), dtype=torch.uint16, device=dev)
+        k_params = torch.zeros((b, s // 128, h_k, 128), dtype=torch.float32, device=dev)
+        v_pack = torch.zeros((b, s, h_k, 32), dtype=torch.uint16, device=dev)
+        v_params = torch.zeros((b, 1, h_k, s), dtype=torch.float32, device=dev)
+        for ib in range(b):
+            k = torch.randn(s, h_k, 128, generator=g, device=dev).half()
+            v = torch.randn(s, h_k, 128, generator=g, device=dev).half()
+            cu = torch.tensor([0, s], dtype=torch.int32, device=dev)
+            mod_pack.kvcache_pack_i4(k, k_pack[ib:ib + 1], k_params[ib:ib + 1], v, v_pack[ib:ib + 1],
+                                     v_params[ib:ib + 1], None, cu, s, "k-channel", 128)
+        caches.append((k_pack, k_params, v_pack, v_params))
+    q = torch.randn(b, 1, h, 128, generator=g, device=dev).half()
+    sc = 1.0 / math.sqrt(128)
+
+    def step(i):
+        c = caches[i % 3]
+        return mod_decode.fwd_kvcache_i4(q, c[0], c[1], c[2], c[3], None, sc, "k-channel", 128, False, -1, -1, 0.0,
+                                         True, 0)
+    for i in range(20):
+        step(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps * 1e3
+
+
 def available(variant: str = "fast") -> bool:
     return os.path.exists(os.path.join(OUT, variant, "bit_decode_cuda_sm100" + sysconfig.get_config_var("EXT_SUFFIX")))
 

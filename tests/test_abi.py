@@ -30,17 +30,18 @@ def test_header_symbols_are_exported():
 
 def test_version_and_error_strings():
     lib = _lib.load()
-    assert lib.bd_version() >= 100
-    for code in range(0, -9, -1):
+    assert lib.bd_version() >= 200
+    for code in range(0, -10, -1):
         assert len(_lib.strerror(code)) > 1
     assert "unknown" in _lib.strerror(-99)
 
 
 def test_struct_sizes_match_the_header_layout():
     # pointers and int64 first, then int32 fields: no padding surprises between ctypes and the C structs
-    assert C.sizeof(_lib.PackArgs) == 2 * 8 + 6 * 8 + 4 * 8 + 6 * 8 + 8 * 4
+    assert C.sizeof(_lib.PackArgs) == 2 * 8 + 6 * 8 + 4 * 8 + 6 * 8 + 9 * 4 + 4      # nine int32 fields, padded to 8
     assert C.sizeof(_lib.DecodeArgs) % 8 == 0
-    assert _lib.DecodeArgs.workspace_bytes.offset == C.sizeof(_lib.DecodeArgs) - 8
+    assert _lib.DecodeArgs.workspace_bytes.offset == C.sizeof(_lib.DecodeArgs) - 16
+    assert _lib.DecodeArgs.test_starve.offset == C.sizeof(_lib.DecodeArgs) - 4
 
 
 def test_argument_validation_needs_no_device():
@@ -63,8 +64,8 @@ def test_argument_validation_needs_no_device():
     assert lib.bd_decode(C.byref(d), None) == -1                   # heads do not divide
     d.h = 8 * 17
     assert lib.bd_decode(C.byref(d), None) == -2                   # more than 16 query heads per KV head
-    d.h, d.group = 32, 32
-    assert lib.bd_decode(C.byref(d), None) == -2                   # group 32 not built
+    d.h, d.group = 32, 16
+    assert lib.bd_decode(C.byref(d), None) == -2                   # group 16 not built
     c = _lib.CombineArgs(n_parts=0)
     assert lib.bd_combine(C.byref(c), None) == -1
 

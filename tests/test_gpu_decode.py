@@ -36,6 +36,7 @@ def _check(x, ref, out, lse, bits, group, dtype, cs=None, rl=None, res=False):
     (2, 128, 40, 8, 512, 0), (4, 128, 2, 2, 128, 0),
     (4, 128, 160, 160, 256, 0),    # more KV heads than SMs: one CTA row, the grid runs in more than one wave
     (2, 128, 320, 160, 512, 0),
+    (4, 32, 32, 8, 2048, 0), (2, 32, 32, 8, 2048, 0), (4, 32, 64, 8, 1024, 2), (2, 32, 8, 8, 512, 0),   # group 32
 ])
 def test_decode_matches_oracle(bits, group, h, h_k, s, splits):
     import bitladder_b200 as B
@@ -54,6 +55,8 @@ def test_decode_matches_oracle(bits, group, h, h_k, s, splits):
     (2, 128, "bf16", 64, 8, 1024, 16, False),
     (4, 64, "fp16", 16, 1, 4096, 256, True),
     (4, 128, "fp16", 8, 8, 256, 1, True),
+    (4, 32, "fp16", 32, 8, 1024, 100, True),
+    (2, 32, "bf16", 16, 2, 1024, 33, True),
 ])
 def test_decode_tail_and_ragged(bits, group, dtype, h, h_k, s, res, ragged):
     import bitladder_b200 as B

@@ -10,14 +10,15 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("bits,group,dtype", [(4, 128, "fp16"), (2, 128, "fp16"), (4, 64, "fp16"),
                                               (2, 64, "fp16"), (4, 128, "bf16"), (2, 128, "bf16"),
-                                              (4, 64, "bf16"), (2, 64, "bf16")])
+                                              (4, 64, "bf16"), (2, 64, "bf16"), (4, 32, "fp16"),
+                                              (2, 32, "fp16"), (4, 32, "bf16"), (2, 32, "bf16")])
 def test_pack_bit_exact(bits, group, dtype):
     import bitladder_b200 as B
     x = H.gen_qkv(2, 1024, 8, 2, seed=11, dtype=dtype)
     G.assert_pack_equal(G.pack_gpu(B, x["k"], x["v"], bits, group), H.oracle_pack(x["k"], x["v"], bits, group, dtype))
 
 
-@pytest.mark.parametrize("bits,group", [(4, 128), (2, 64)])
+@pytest.mark.parametrize("bits,group", [(4, 128), (2, 64), (4, 32), (2, 32)])
 def test_pack_edge_values(bits, group):
     """All-zero and constant groups (scale 0), fp16 max, huge and tiny magnitudes, outlier channels."""
     import bitladder_b200 as B

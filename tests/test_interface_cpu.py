@@ -41,7 +41,7 @@ def test_cpu_tensors_are_rejected():
 @pytest.mark.parametrize("kw,msg", [
     (dict(quant_mode="k-tensor"), "quant_mode"),
     (dict(num_bits=8), "num_bits"),
-    (dict(group_size=32), "group_size"),
+    (dict(group_size=16), "group_size"),
 ])
 def test_unsupported_configs_raise_instead_of_doing_nothing(kw, msg):
     k = torch.zeros(1, 128, 2, 128, dtype=torch.float16)
