@@ -7,8 +7,10 @@ Only when ONE long sequence is split along its tokens is there an exchange step:
 each rank attends over its token range and the ranks merge their partial
 ``(out, lse)`` with the log-sum-exp rule of the reference's split combine
 (``csrc/bit_decode/src/flash_fwd_kernel.h:1217-1231, 1280-1298``).  The exchange is
-tiny (``b*h*129*4`` bytes per rank) and latency-bound; it is an all-gather (NCCL
-on GPUs, gloo in the CPU tests) followed by the local ``bd_combine`` kernel.
+tiny (``b*h*129*4`` bytes per rank) and latency-bound.  On GPUs it is one kernel per rank
+that stores the partial into the peers' memory, waits for theirs and merges
+(``PeerExchange`` / ``bd_exchange_combine``); the portable form is an all-gather (NCCL,
+or gloo in the CPU tests) followed by the local ``bd_combine`` kernel.
 
 Nothing here allocates per step beyond the gathered partials; the helpers that
 slice caches are meant for set-up time.
@@ -26,7 +28,7 @@ from .bit_decode_interface import (DecodeStep, _dtype_code, _stream, combine_par
                                    pack_block_tokens)
 
 __all__ = ["shard_range", "shard_batch", "shard_kv_heads", "sequence_shard_bounds",
-           "gather_partials", "decode_sequence_parallel", "SequenceParallelStep"]
+           "gather_partials", "decode_sequence_parallel", "SequenceParallelStep", "PeerExchange"]
 
 
 def shard_range(n: int, rank: int, world: int) -> Tuple[int, int]:
@@ -107,16 +109,83 @@ def decode_sequence_parallel(q, k_pack, k_params, v_pack, v_params, softmax_scal
     return combine_partials(outs, lses, out_dtype=out_dtype or q.dtype, return_lse=return_lse)
 
 
+class PeerExchange:
+    """The exchange areas of a sequence split, one per rank, mapped into every rank (CUDA IPC).
+
+    Set-up only: ``PeerExchange(rows, group)`` allocates this rank's area through the library
+    (``bd_peer_alloc``), passes its 64-byte handle to the other ranks with an ``all_gather_object`` (host
+    side, any backend) and maps theirs.  One process per GPU.  ``close()`` unmaps and frees; call it
+    with all ranks quiesced."""
+
+    def __init__(self, rows: int, group=None, device=None):
+        import torch.distributed as dist
+
+        lib = _lib.load()
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > _lib.BD_MAX_PARTS:
+            raise RuntimeError(f"at most {_lib.BD_MAX_PARTS} ranks can share a sequence")
+        self.rows = rows
+        self._dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.bytes = int(lib.bd_exchange_area_bytes(self.world, rows))
+        with torch.cuda.device(self._dev):
+            mine = C.c_void_p()
+            _lib.check(lib.bd_peer_alloc(self.bytes, C.byref(mine)), "bd_peer_alloc")
+            handle = (C.c_ubyte * 64)()
+            _lib.check(lib.bd_peer_export(mine, handle), "bd_peer_export")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            self.areas = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    self.areas.append(mine.value)
+                    continue
+                buf = (C.c_ubyte * 64).from_buffer_copy(h)
+                ptr = C.c_void_p()
+                _lib.check(lib.bd_peer_open(buf, C.byref(ptr)), "bd_peer_open")
+                self.areas.append(ptr.value)
+        self._mine = mine.value
+        self.c_areas = (C.c_void_p * self.world)(*self.areas)
+        self._group = group
+
+    def state(self):
+        """Wait for the current stream; returns (status, epoch) of this rank's area and clears the status."""
+        epoch = C.c_uint32()
+        with torch.cuda.device(self._dev):
+            rc = int(_lib.load().bd_exchange_state(self._mine, _stream(self._dev), C.byref(epoch)))
+        return rc, int(epoch.value)
+
+    def close(self):
+        lib = _lib.load()
+        with torch.cuda.device(self._dev):
+            torch.cuda.synchronize()
+            for r, ptr in enumerate(self.areas):
+                if ptr is None:
+                    continue
+                if r == self.rank:
+                    lib.bd_peer_free(ptr)
+                else:
+                    lib.bd_peer_close(ptr)
+        self.areas = [None] * self.world
+
+
 class SequenceParallelStep:
-    """``decode_sequence_parallel`` prepared once for a decoder loop: the local partial, the gathered
-    partials of all ranks and the result live in buffers allocated here, the local step is a
-    ``DecodeStep``, the exchange is ONE ``all_gather_into_tensor`` of ``b*h*(d+1)`` fp32 values per rank
-    (each rank's normalised output rows followed by their log-sum-exps) and the merge one ``bd_combine``
-    launch over pointers into the gathered buffer.  ``step()`` returns the full result on every rank."""
+    """``decode_sequence_parallel`` prepared once for a decoder loop.
+
+    The local step is a ``DecodeStep`` that writes this rank's fp32 partial and its log-sum-exps; then
+
+    * ``exchange="peer"`` (default on GPUs): ONE kernel (``bd_exchange_combine``) stores the partial into
+      every peer's exchange area over NVLink, waits (bounded) for the peers' partials in its own area and
+      merges them.  No NCCL call on the step, nothing allocated, capturable in a CUDA graph
+      (``capturable``).  A peer that does not publish makes the kernel give up after ``spin_limit`` polls
+      and leave ``BD_ERR_TIMEOUT`` in the area's status word (``check()`` raises then).
+    * ``exchange="nccl"``: one ``all_gather_into_tensor`` of ``b*h*(d+1)`` fp32 values per rank and one
+      ``bd_combine`` launch over pointers into the gathered buffer.
+
+    ``step()`` returns the full result on every rank."""
 
     def __init__(self, q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size=128, num_bits=4, *,
                  seqlen_k=None, k_res=None, v_res=None, res_lens=None, cache_seqlens=None, group=None,
-                 out_dtype=None):
+                 out_dtype=None, exchange="peer", spin_limit=0):
         import torch.distributed as dist
 
         self._dist, self._group = dist, group
@@ -124,25 +193,60 @@ class SequenceParallelStep:
         if world > _lib.BD_MAX_PARTS:
             raise RuntimeError(f"at most {_lib.BD_MAX_PARTS} ranks can share a sequence")
         b, _, h, d = q.shape
-        n_out, n = b * h * d, b * h * (d + 1)
+        rows = b * h
+        n_out = rows * d
+        lse_off = (n_out + 3) // 4 * 4                 # both parts of a rank's record start on 16 bytes
+        n = lse_off + (rows + 3) // 4 * 4
         dev = q.device
+        self._dev = dev
         self._local = torch.empty(n, dtype=torch.float32, device=dev)
-        self._gathered = torch.empty(world * n, dtype=torch.float32, device=dev)
         self._local_step = DecodeStep(q, k_pack, k_params, v_pack, v_params, None, softmax_scale, "k-channel",
                                       group_size, num_bits, seqlen_k=seqlen_k, k_res=k_res, v_res=v_res,
                                       res_lens=res_lens, cache_seqlens=cache_seqlens,
-                                      out=self._local[:n_out].view(b, 1, h, d), lse=self._local[n_out:])
+                                      out=self._local[:n_out].view(b, 1, h, d), lse=self._local[lse_off:lse_off + rows])
         self.out = torch.empty((b, 1, h, d), dtype=out_dtype or q.dtype, device=dev)
-        base = self._gathered.data_ptr()
-        self._po = (C.c_void_p * world)(*[base + 4 * (r * n) for r in range(world)])
-        self._pl = (C.c_void_p * world)(*[base + 4 * (r * n + n_out) for r in range(world)])
-        self._args = _lib.CombineArgs(n_parts=world, part_out=C.cast(self._po, C.POINTER(C.c_void_p)),
-                                      part_lse=C.cast(self._pl, C.POINTER(C.c_void_p)), rows=b * h, d=d,
-                                      out=self.out.data_ptr(), lse=None, out_dtype=_dtype_code(self.out.dtype))
-        self._dev = dev
+        self.kind = exchange
+        if exchange == "peer":
+            self.peers = PeerExchange(rows, group, dev)
+            self._xargs = _lib.ExchangeArgs(rank=self.peers.rank, world=world,
+                                            areas=C.cast(self.peers.c_areas, C.POINTER(C.c_void_p)),
+                                            part_out=self._local.data_ptr(), part_lse=self._local.data_ptr() + 4 * lse_off,
+                                            rows=rows, d=d, out=self.out.data_ptr(), lse=None,
+                                            out_dtype=_dtype_code(self.out.dtype), spin_limit=int(spin_limit))
+            self.capturable = True
+            self.exchange = {"kind": "peer stores into mapped exchange areas + flags, merged in the same kernel",
+                             "launches": 1, "bytes_per_rank_per_peer": 4 * (n_out + rows)}
+        elif exchange == "nccl":
+            self._gathered = torch.empty(world * n, dtype=torch.float32, device=dev)
+            base = self._gathered.data_ptr()
+            self._po = (C.c_void_p * world)(*[base + 4 * (r * n) for r in range(world)])
+            self._pl = (C.c_void_p * world)(*[base + 4 * (r * n + lse_off) for r in range(world)])
+            self._args = _lib.CombineArgs(n_parts=world, part_out=C.cast(self._po, C.POINTER(C.c_void_p)),
+                                          part_lse=C.cast(self._pl, C.POINTER(C.c_void_p)), rows=rows, d=d,
+                                          out=self.out.data_ptr(), lse=None, out_dtype=_dtype_code(self.out.dtype))
+            self.capturable = False
+            self.exchange = {"kind": "NCCL all_gather_into_tensor + bd_combine", "launches": 2,
+                             "bytes_per_rank_per_peer": 4 * n}
+        else:
+            raise ValueError("exchange must be 'peer' or 'nccl'")
 
     def step(self):
         self._local_step.step()
-        self._dist.all_gather_into_tensor(self._gathered, self._local, group=self._group)
-        _lib.check(_lib.load().bd_combine(C.byref(self._args), _stream(self._dev)), "bd_combine")
+        with torch.cuda.device(self._dev):
+            if self.kind == "peer":
+                _lib.check(_lib.load().bd_exchange_combine(C.byref(self._xargs), _stream(self._dev)), "bd_exchange_combine")
+            else:
+                self._dist.all_gather_into_tensor(self._gathered, self._local, group=self._group)
+                _lib.check(_lib.load().bd_combine(C.byref(self._args), _stream(self._dev)), "bd_combine")
         return self.out
+
+    def check(self):
+        """Wait for the stream and raise if a step's exchange gave up waiting for a peer."""
+        if self.kind == "peer":
+            rc, _ = self.peers.state()
+            if rc != 0:
+                raise RuntimeError(f"sequence-parallel step failed on the device: {_lib.strerror(rc)} (code {rc})")
+
+    def close(self):
+        if self.kind == "peer":
+            self.peers.close()

@@ -21,7 +21,22 @@ def test_reference_arm_prints_the_contract_line():
     e2e = line["e2e"]
     assert e2e["value"] == line["value"] and e2e["unit"] == line["unit"]
     assert e2e["h2d_bytes_per_step"] == 0 and e2e["d2h_bytes_per_step"] == 0
-    assert "workload" in line["config"]
+    assert "workload" in line["config"] and line["config"]["global_batch"] == 1 and line["config"]["n_shards"] == 1
+    assert line["steps"] == 1 and line["warmup"] == 0 and line["scaling"] == "strong"
+
+
+def test_both_arms_name_the_job_the_same_way():
+    sys.path.insert(0, ROOT)
+    import bench
+    for n in (1, 2, 8):
+        cfg = bench.job_config("C2", bench.WORKLOADS["C2"], n)
+        assert cfg["global_batch"] == 8 and cfg["n_shards"] == n          # the same job at every N: strong scaling
+    sh = [bench.Shard(bench.WORKLOADS["C2"], r, 8) for r in range(8)]
+    assert [s.b for s in sh] == [1] * 8 and sh[3].b_lo == 3
+    sh = [bench.Shard(bench.WORKLOADS["C4"], r, 4) for r in range(4)]
+    assert [s.h_k for s in sh] == [8] * 4 and sh[0].b == 32
+    sh = [bench.Shard(bench.WORKLOADS["C5b"], r, 8) for r in range(8)]
+    assert [s.s for s in sh] == [131072] * 8 and sh[7].t_hi == 1048576
 
 
 def test_workload_table_matches_the_baseline_configs():

@@ -1,10 +1,12 @@
 """Two GPUs, one process each, NCCL: the sharded decode paths on real devices.
 
 Skipped on a box with fewer than two GPUs.  Each rank runs as a child process
-(``torch.multiprocessing.spawn``), the only exchange on the data path is the
-all-gather of the per-rank partial ``(out, lse)`` of the sequence split; batch
-shards need none.  NVLS is switched off for NCCL (plain ring/tree over NVLink is
-all a 33 KB all-gather needs).  The result of every rank is compared with the CPU
+(``torch.multiprocessing.spawn``), the only exchange on the data path is that of
+the per-rank partial ``(out, lse)`` of the sequence split (once as an NCCL
+all-gather, once as plain stores into peer-mapped exchange areas); batch shards
+need none.  NVLS is switched off for NCCL and the library's own kernel uses plain
+peer stores, no multimem.  The failure test makes its failure on the host: a rank
+skips a step between two steps.  The result of every rank is compared with the CPU
 oracle over the whole sequence, to the tolerance of the single-GPU parity tests."""
 import math
 import os
@@ -54,12 +56,49 @@ def _rank_main(rank, world, port, x, ref_seq, ref_batch, bits, group, res):
                                               return_lse=True, **kw)
         err = np.abs(out.float().cpu().numpy()[:, 0] - ref_seq).max()
         assert err <= 2e-3, ("sequence split", rank, err)
-        # the same exchange prepared once (one all-gather of a packed buffer, one merge launch)
-        sp = S.SequenceParallelStep(x["q"].to(dev), *bufs, scale, group, bits, seqlen_k=n, **kw)
-        for _ in range(2):
-            out2 = sp.step()
-            err = np.abs(out2.float().cpu().numpy()[:, 0] - ref_seq).max()
-            assert err <= 2e-3, ("prepared sequence split", rank, err)
+        # the same exchange prepared once: over NCCL (one all-gather of a packed buffer, one merge launch) and
+        # over peer-mapped exchange areas (one kernel stores, waits and merges), eagerly and as a CUDA graph
+        for kind in ("nccl", "peer"):
+            sp = S.SequenceParallelStep(x["q"].to(dev), *bufs, scale, group, bits, seqlen_k=n, exchange=kind, **kw)
+            for _ in range(3):
+                out2 = sp.step()
+                err = np.abs(out2.float().cpu().numpy()[:, 0] - ref_seq).max()
+                assert err <= 2e-3, ("prepared sequence split", kind, rank, err)
+            if kind == "peer":
+                sp.check()
+                gr = torch.cuda.CUDAGraph()
+                side = torch.cuda.Stream(dev)
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    with torch.cuda.graph(gr, stream=side):
+                        sp.step()
+                        sp.step()
+                torch.cuda.current_stream().wait_stream(side)
+                for _ in range(3):
+                    sp.out.zero_()
+                    gr.replay()
+                    err = np.abs(sp.out.float().cpu().numpy()[:, 0] - ref_seq).max()
+                    assert err <= 2e-3, ("graph replay of the peer exchange", rank, err)
+                sp.check()
+                dist.barrier()
+                # a peer that skips a step (a failure made on the host, between steps): the other rank's
+                # bounded wait runs out and its area reports it; nothing faults or hangs
+                sp2 = S.SequenceParallelStep(x["q"].to(dev), *bufs, scale, group, bits, seqlen_k=n, exchange="peer",
+                                             spin_limit=20000, **kw)
+                sp2.step()
+                sp2.check()
+                dist.barrier()
+                if rank == 0:
+                    sp2.step()
+                    try:
+                        sp2.check()
+                        raise AssertionError("the missing peer was not noticed")
+                    except RuntimeError as exc:
+                        assert "wait" in str(exc)
+                torch.cuda.synchronize()
+                dist.barrier()
+                sp2.close()
+                sp.close()
 
         # ---- batch split: rank r holds sequences [lo, hi); no communication at all
         lo, hi = S.shard_range(b, rank, world)
