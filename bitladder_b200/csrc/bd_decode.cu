@@ -53,17 +53,22 @@ namespace bd {
 #ifdef BD_TRACE
 // Timing trace for development builds only (-DBD_TRACE): per CTA its SM, start, the time every warp
 // left the streaming loop, and the CTA's end, in nanoseconds of the global timer.
-__device__ unsigned long long g_trace[4096 * 16];
+__device__ unsigned long long g_trace[4096 * 32];
 __device__ __forceinline__ unsigned long long trace_now() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
+#define BD_TRACE_MARK(slot) do { if (lane == 0 && blockIdx.x < 4096) g_trace[blockIdx.x * 32 + (slot)] = trace_now(); } while (0)
 __device__ __forceinline__ unsigned trace_smid() {
     unsigned r;
     asm volatile("mov.u32 %0, %smid;" : "=r"(r));
     return r;
 }
+#endif
+
+#ifndef BD_TRACE
+#define BD_TRACE_MARK(slot) do { } while (0)
 #endif
 
 #ifndef BD_MAX_WARPS
@@ -94,7 +99,7 @@ struct Cfg {
     static constexpr int NACC = 8 * NQT * 4 + 4 * NQT;  // floats per thread handed over in a merge
     // per warp: one K tile and one V tile, then their scales/zeros
     static constexpr int WARP_BYTES = 2 * CODE_BYTES + 2 * PRM_BYTES + 16;
-    static constexpr int FIT = (kSmemLimit - 32) / (WARP_BYTES + 4);
+    static constexpr int FIT = (kSmemLimit - 32) / (WARP_BYTES + 32);
     // eight fields per word (2 bits) and two query tiles both need more than the 168 registers
     // twelve warps leave a thread: eight warps (255 registers) measured 3-4 % faster at 2 bits
     // (the same holds for group 32, with four parameter sets per block)
@@ -103,8 +108,9 @@ struct Cfg {
     static constexpr int THREADS = WARPS * 32;
     static constexpr size_t OFF_PRM = size_t(WARPS) * 2 * CODE_BYTES;
     static constexpr size_t OFF_BAR = OFF_PRM + size_t(WARPS) * 2 * PRM_BYTES;
-    static constexpr size_t OFF_FLAGS = OFF_BAR + 2 * WARPS * 8;            // abort flag, then arrivals[WARPS]
-    static constexpr size_t SMEM = OFF_FLAGS + 16 + WARPS * 4;
+    static constexpr size_t OFF_FLAGS = OFF_BAR + 2 * WARPS * 8;            // abort flag, arrivals[WARPS], segment notes[WARPS][4]
+    static constexpr size_t OFF_NOTES = OFF_FLAGS + 16 + ((WARPS * 4 + 15) / 16) * 16;
+    static constexpr size_t SMEM = OFF_NOTES + WARPS * 16;
     static constexpr int DEPOSIT_FLOATS = NACC * 32;                        // one warp's share of a segment
     static_assert(DEPOSIT_FLOATS * 4 <= 2 * CODE_BYTES, "a deposit fits the warp's own tile slots");
     static constexpr int CTAS_PER_SM = (SMEM + 1024) * 3 <= 233472 ? 3 : ((SMEM + 1024) * 2 <= 233472 ? 2 : 1);
@@ -295,10 +301,11 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int ih = blockIdx.x % p.h_k, row = blockIdx.x / p.h_k;
     const int g = lane >> 2, l = lane & 3;
+    int4 *note = reinterpret_cast<int4 *>(smem + C::OFF_NOTES) + warp;       // this warp's notes on its current segment
 #ifdef BD_TRACE
     if (tid == 0 && blockIdx.x < 4096) {
-        g_trace[blockIdx.x * 16 + 0] = trace_smid();
-        g_trace[blockIdx.x * 16 + 1] = trace_now();
+        g_trace[blockIdx.x * 32 + 0] = trace_smid();
+        g_trace[blockIdx.x * 32 + 1] = trace_now();
     }
 #endif
     if ((smem_base & 1023u) != 0) {                      // never seen; refuse rather than read garbage
@@ -445,6 +452,35 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             const uint2 vw = __ldg(reinterpret_cast<const uint2 *>(static_cast<const uint16_t *>(p.v_new) + src));
             *reinterpret_cast<uint2 *>(static_cast<uint16_t *>(p.k_res_out) + dst) = kw;
             *reinterpret_cast<uint2 *>(static_cast<uint16_t *>(p.v_res_out) + dst) = vw;
+        }
+
+        // Which warps of this CTA share the sequence, which of them goes on with another sequence
+        // afterwards, and how many CTA rows hold a part of it: worked out now, while the first copies
+        // are in flight, and kept in shared memory (not in registers across the streaming loop).
+        {
+            const int64_t Tw = wpart.total();
+            const int64_t seq_first = wpart.first(ib), seq_end = seq_first + wpart.count(ib);
+            uint32_t share_mask = 0;
+            int goes_on = -1;
+            int64_t lo = wpart.row_begin(int64_t(row) * kWarps, Tw);
+#pragma unroll 1
+            for (int w = 0; w < kWarps; ++w) {
+                const int64_t hi = wpart.row_begin(int64_t(row) * kWarps + w + 1, Tw);
+                if (max(lo, seq_first) < min(hi, seq_end)) {
+                    share_mask |= 1u << w;
+                    if (hi > seq_end) goes_on = w;
+                }
+                lo = hi;
+            }
+            const PartRange pr = part_range(p.part, ib);
+            int nparts = pr.c1 - pr.c0 + 1;
+            if (!pr.dense) {
+                nparts = 0;
+                for (int c = pr.c0; c <= pr.c1; ++c) nparts += row_has_part(p.part, ib, c) ? 1 : 0;
+            }
+            if (lane == 0)
+                *note = make_int4(int(share_mask), (goes_on + 1) | ((pr.c1 - pr.c0 + 1) << 8), pr.c0, (nparts << 1) | (pr.dense ? 1 : 0));
+            __syncwarp();
         }
 
         // Query rows as B fragments: thread (g, l) holds q[row g][32a + 8l .. +7], a = 0..3.
@@ -869,19 +905,12 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
         }
         if (aborted) *abort_flag = 1;
 #ifdef BD_TRACE
-        if (lane == 0 && blockIdx.x < 4096 && warp < 13) g_trace[blockIdx.x * 16 + 2 + warp] = trace_now();
+        if (lane == 0 && blockIdx.x < 4096 && warp < 13) g_trace[blockIdx.x * 32 + 2 + warp] = trace_now();
 #endif
 
         // ------------------------------------------------------------------
-        // End of this warp's share of the sequence.  The warps of the CTA whose ranges
-        // hold units of it each deposit their partial (O, m, l in the fragment layout, the
-        // same in every warp) and count in; no warp waits for another.  The one that counts
-        // in last merges the deposits in warp order (so the result does not depend on who
-        // was last) and finishes the segment.  A warp whose range ends inside the sequence
-        // has nothing left to stream and deposits into its own tile slots in shared memory;
-        // the one warp in whose range the sequence ends goes on with the next sequence, its
-        // tile slots already receive those blocks, and its deposit goes through global
-        // memory (at most one such deposit per sequence and KV head).
+        // End of this warp's share of the sequence: its partial (O, m, l in the fragment layout, the
+        // same in every warp) in final units.
         // ------------------------------------------------------------------
         float acc[NACC];       // O in final units (field weights and zero sums applied), then m, l
 #pragma unroll
@@ -911,29 +940,18 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                 acc[32 * NQT + nq * 4 + 2 + c] = sum;
             }
         }
-        // Which warps of this CTA share the sequence, and which of them goes on afterwards.
-        const int64_t Tw = wpart.total();
-        const int64_t seq_first = wpart.first(ib), seq_end = seq_first + wpart.count(ib);
-        uint32_t share_mask = 0;
-        int goes_on = -1;
-        {
-            int64_t lo = wpart.row_begin(int64_t(row) * kWarps, Tw);
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) {
-                const int64_t hi = wpart.row_begin(int64_t(row) * kWarps + w + 1, Tw);
-                if (max(lo, seq_first) < min(hi, seq_end)) {
-                    share_mask |= 1u << w;
-                    if (hi > seq_end) goes_on = w;
-                }
-                lo = hi;
-            }
-        }
+        // The warps that share the sequence each deposit their partial and count in; the one that counts
+        // in last folds the deposits in warp order (so the result does not depend on who was last).  A
+        // warp whose range ends inside the sequence deposits into its own tile slots; the one warp in
+        // whose range the sequence ends goes on streaming and deposits through global memory.
+        const int4 nt = *note;
+        const uint32_t share_mask = uint32_t(nt.x);
+        const int goes_on = (nt.y & 0xff) - 1;
         const int nshare = __popc(share_mask);
         bool finisher = true;
         if (nshare > 1) {
-            const bool to_global = goes_on == warp;
             float *gdep = p.warp_acc + (int64_t(ib) * p.h_k + ih) * C::DEPOSIT_FLOATS;
-            if (to_global) {
+            if (goes_on == warp) {
 #pragma unroll
                 for (int i = 0; i < NACC; ++i) __stcg(gdep + i * 32 + lane, acc[i]);
                 __threadfence();
@@ -949,67 +967,56 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             old = __shfl_sync(0xffffffffu, old, 0);
             finisher = old == nshare - 1;
             if (finisher) {
+                BD_TRACE_MARK(16);
                 if (goes_on >= 0) __threadfence(); else __threadfence_block();
-                // The deposits sit in this CTA's shared memory or (one warp's) in global memory,
-                // written past L1 and never read before in this launch: generic loads serve both.
+                // generic loads serve shared and (written past L1, never read before) global deposits
                 auto deposit_of = [&](int w) {
                     return (w == goes_on) ? static_cast<const float *>(gdep)
                                           : reinterpret_cast<const float *>(smem + size_t(w) * 2 * C::CODE_BYTES);
                 };
-                // pass 1: the column maxima over all deposits
-                float mx[NQT][2];
-#pragma unroll
-                for (int nq = 0; nq < NQT; ++nq) mx[nq][0] = mx[nq][1] = -INFINITY;
-#pragma unroll 4
-                for (int w = 0; w < kWarps; ++w) {
-                    if (((share_mask >> w) & 1u) == 0) continue;
+                uint32_t rest = share_mask;
+                int w = __ffs(rest) - 1;
+                rest &= rest - 1;
+                {
                     const float *dep = deposit_of(w);
 #pragma unroll
-                    for (int nq = 0; nq < NQT; ++nq)
-#pragma unroll
-                        for (int c = 0; c < 2; ++c)
-                            mx[nq][c] = fmaxf(mx[nq][c], dep[(32 * NQT + nq * 4 + c) * 32 + lane]);
+                    for (int i = 0; i < NACC; ++i) acc[i] = dep[i * 32 + lane];
                 }
-                // pass 2: the weighted sum in warp order (every term independent of the others
-                // but for the running sums, so the loads and exponentials overlap)
-#pragma unroll
-                for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
-#pragma unroll 2
-                for (int w = 0; w < kWarps; ++w) {
-                    if (((share_mask >> w) & 1u) == 0) continue;
+#pragma unroll 1
+                while (rest) {
+                    w = __ffs(rest) - 1;
+                    rest &= rest - 1;
                     const float *dep = deposit_of(w);
                     float v[NACC];
 #pragma unroll
                     for (int i = 0; i < NACC; ++i) v[i] = dep[i * 32 + lane];
 #pragma unroll
                     for (int nq = 0; nq < NQT; ++nq) {
-                        float f[2];
+                        float fa[2], fv[2];
 #pragma unroll
                         for (int c = 0; c < 2; ++c) {
-                            const float mw = v[32 * NQT + nq * 4 + c];
-                            f[c] = (mw == -INFINITY) ? 0.f : ex2f(mw - mx[nq][c]);
-                            acc[32 * NQT + nq * 4 + 2 + c] = fmaf(f[c], v[32 * NQT + nq * 4 + 2 + c], acc[32 * NQT + nq * 4 + 2 + c]);
+                            const float ma = acc[32 * NQT + nq * 4 + c], mv = v[32 * NQT + nq * 4 + c];
+                            const float mx = fmaxf(ma, mv);
+                            fa[c] = (ma == -INFINITY) ? 0.f : ex2f(ma - mx);
+                            fv[c] = (mv == -INFINITY) ? 0.f : ex2f(mv - mx);
+                            acc[32 * NQT + nq * 4 + c] = mx;
+                            acc[32 * NQT + nq * 4 + 2 + c] =
+                                fmaf(fv[c], v[32 * NQT + nq * 4 + 2 + c], fa[c] * acc[32 * NQT + nq * 4 + 2 + c]);
                         }
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) acc[nq * 32 + i] = fmaf(f[i & 1], v[nq * 32 + i], acc[nq * 32 + i]);
+                        for (int i = 0; i < 32; ++i) acc[nq * 32 + i] = fmaf(fv[i & 1], v[nq * 32 + i], fa[i & 1] * acc[nq * 32 + i]);
                     }
-                }
-#pragma unroll
-                for (int nq = 0; nq < NQT; ++nq) {
-                    acc[32 * NQT + nq * 4 + 0] = mx[nq][0];
-                    acc[32 * NQT + nq * 4 + 1] = mx[nq][1];
                 }
             }
         }
         if (finisher) {
+            BD_TRACE_MARK(17);
             // How many rows hold a part of this sequence?  One: this is the final result.
             // More: leave a normalised partial; the row that arrives last merges them all.
-            const PartRange pr = part_range(p.part, ib);
-            int nparts = pr.c1 - pr.c0 + 1;
-            if (!pr.dense) {
-                nparts = 0;
-                for (int c = pr.c0; c <= pr.c1; ++c) nparts += row_has_part(p.part, ib, c) ? 1 : 0;
-            }
+            const int nparts = nt.w >> 1;
+            PartRange pr;
+            pr.c0 = nt.z; pr.dense = (nt.w & 1) != 0;
+            pr.c1 = pr.c0 + (nt.y >> 8) - 1;
             const bool final_here = nparts <= 1;
             const int64_t slot = (int64_t(row) + ib) * p.h_k + ih;
             // normalise in place, then one straight run of stores per destination kind
@@ -1074,6 +1081,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                 int old = 0;
                 if (lane == 0) old = atomicAdd(p.counters + int64_t(ib) * p.h_k + ih, 1);
                 old = __shfl_sync(0xffffffffu, old, 0);
+                BD_TRACE_MARK(18);
                 if (old == nparts - 1) {
                     __threadfence();
                     // Parts sit in consecutive rows, so consecutive slots h_k apart (rows that
@@ -1212,6 +1220,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                     }
                     }
                     if (lane == 0) p.counters[int64_t(ib) * p.h_k + ih] = 0;   // ready for the next step
+                    BD_TRACE_MARK(19);
                 }
             }
         }
@@ -1224,7 +1233,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     // ======================================================================
     __syncthreads();
 #ifdef BD_TRACE
-    if (tid == 0 && blockIdx.x < 4096) g_trace[blockIdx.x * 16 + 15] = trace_now();
+    if (tid == 0 && blockIdx.x < 4096) g_trace[blockIdx.x * 32 + 15] = trace_now();
 #endif
     if (*abort_flag != 0) {
         if (tid == 0) atomicExch(p.status, BD_ERR_TIMEOUT);
