@@ -180,7 +180,7 @@ def kvcache_pack_int(k_cache: torch.Tensor, k_pack: torch.Tensor, k_params: torc
 
 def _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
                  k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, lse, num_splits, block_table=None,
-                 k_new=None, v_new=None, spin_limit=0, test_starve=0):
+                 k_new=None, v_new=None, spin_limit=0, test_starve=0, advance=False):
     b, s_cap, h_k, d = _check_packed(k_pack, k_params, v_pack, v_params, num_bits, group_size)
     _require(q.dim() == 4 and q.shape[1] == 1, "q must be (b, 1, h, d): one query token per sequence")
     num_pages = 0
@@ -247,6 +247,12 @@ def _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_siz
     a.softmax_scale = float(softmax_scale)
     a.num_splits = int(num_splits)
     a.spin_limit, a.test_starve = int(spin_limit), int(test_starve)
+    if advance:
+        _require(k_new is not None and cache_seqlens is not None and res_lens is not None and block_table is None,
+                 "advance needs k_new/v_new, cache_seqlens and res_lens, and a cache without a block table")
+        _require(k_res.shape[1] >= pack_block_tokens(num_bits),
+                 f"advance needs a tail buffer of at least {pack_block_tokens(num_bits)} rows (one pack block)")
+        a.advance = 1
     return a
 
 
@@ -290,7 +296,7 @@ def fwd_kvcache_int(q: torch.Tensor,
                     out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
                     workspace: Optional[torch.Tensor] = None, num_splits: int = 0,
                     k_new: Optional[torch.Tensor] = None, v_new: Optional[torch.Tensor] = None,
-                    check: bool = False, spin_limit: int = 0, _test_starve: int = 0):
+                    check: bool = False, spin_limit: int = 0, _test_starve: int = 0, advance: bool = False):
     """One decode-attention step over the packed cache; returns ``out`` (b, 1, h, d).
 
     Same positional signature as the reference (``bit_decode_interface.py:43-86``),
@@ -307,7 +313,11 @@ def fwd_kvcache_int(q: torch.Tensor,
     with changes); ``k_new``/``v_new`` (b, 1, h_k, d): the K/V rows of the token decoded in this
     step — the step attends over them as the next tail row and stores them at row ``res_lens[b]`` of
     ``k_res``/``v_res`` (fused append; the caller then adds one to ``res_lens``, which must be below
-    the tail buffers' length).  Asynchronous on the current stream, unless ``check=True``: then the
+    the tail buffers' length); with ``advance=True`` the library does that bookkeeping on the device
+    instead: after the step ``res_lens`` is one larger, and a tail that has reached one pack block is
+    quantize-packed as the sequence's next block, ``cache_seqlens`` grows by that block and ``res_lens``
+    starts again at 0 (the roll-over of the reference's residual scheme), so a decoder step needs no host
+    logic and can be captured in a CUDA graph.  Asynchronous on the current stream, unless ``check=True``: then the
     call waits for the step and raises ``RuntimeError`` if the kernel reported an error (a device-side
     wait on a copy that ran out after ``spin_limit`` polls, 0 = the library's default of seconds; a
     ``opt_block_table`` entry outside the page pool).  Without ``check`` such a step returns
@@ -324,7 +334,7 @@ def fwd_kvcache_int(q: torch.Tensor,
     lse = torch.empty((q.shape[0], q.shape[2]), dtype=torch.float32, device=q.device) if return_lse else None
     a = _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
                      k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, lse, num_splits, opt_block_table,
-                     k_new, v_new, spin_limit, _test_starve)
+                     k_new, v_new, spin_limit, _test_starve, advance)
     with torch.cuda.device(q.device):
         ws = _workspace_for(a, q.device, workspace)
         _lib.check(_lib.load().bd_decode(C.byref(a), _stream(q.device)), "bd_decode")
@@ -359,7 +369,7 @@ class DecodeStep:
     def __init__(self, q, k_pack, k_params, v_pack, v_params, opt_block_table=None, softmax_scale=1.0,
                  quant_mode="k-channel", group_size=128, num_bits=4, *, k_res=None, v_res=None, res_lens=None,
                  cache_seqlens=None, seqlen_k=None, return_lse=False, out=None, out_dtype=None, num_splits=0,
-                 k_new=None, v_new=None, lse=None, spin_limit=0, _test_starve=0):
+                 k_new=None, v_new=None, lse=None, spin_limit=0, _test_starve=0, advance=False):
         _check_config(quant_mode, group_size, num_bits)
         _check_cuda(q, k_pack, k_params, v_pack, v_params, k_res, v_res, res_lens, cache_seqlens, out,
                     opt_block_table, k_new, v_new)
@@ -379,7 +389,7 @@ class DecodeStep:
                         if return_lse else None)
         self._args = _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
                                   k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, self.lse, num_splits,
-                                  opt_block_table, k_new, v_new, spin_limit, _test_starve)
+                                  opt_block_table, k_new, v_new, spin_limit, _test_starve, advance)
         self._device = q.device
         with torch.cuda.device(q.device):
             need = int(_lib.load().bd_decode_workspace_bytes(C.byref(self._args)))

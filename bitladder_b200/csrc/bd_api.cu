@@ -166,6 +166,10 @@ int check_decode_args(const bd_decode_args *a) {
     if (a->k_new && (!aligned16(a->k_new) || !aligned16(a->v_new) || a->new_stride_b % 8 || a->new_stride_h % 8))
         return BD_ERR_ALIGNMENT;
     if (a->k_res && (a->res_len < 0 || a->res_len > 256)) return BD_ERR_UNSUPPORTED;
+    if (a->advance) {      // device-side bookkeeping: appends, ragged lengths, a tail that holds a pack block, no pages
+        if (!a->k_new || !a->cache_seqlens || !a->res_lens || a->block_table) return BD_ERR_INVALID;
+        if (a->res_len < pack_block_tokens(a->bits) || a->b > 65535) return BD_ERR_INVALID;
+    }
     if (!aligned16(a->q) || !aligned16(a->out) || !aligned16(a->k_pack) || !aligned16(a->k_params) ||
         !aligned16(a->v_pack) || !aligned16(a->v_params))
         return BD_ERR_ALIGNMENT;
@@ -270,6 +274,7 @@ const char *bd_strerror(int code) {
         case BD_ERR_CUDA: return "a CUDA runtime or driver call failed";
         case BD_ERR_DEVICE: return "device is not compute capability 10.x";
         case BD_ERR_TIMEOUT: return "a bounded wait inside a kernel ran out";
+        case BD_ERR_CAPACITY: return "a tail filled up but the packed buffers have no room for another block";
         case BD_ERR_PAGE: return "a block_table entry lies outside [0, num_pages); its tokens were left out";
         case BD_ERR_SCRATCH_LIMIT: return "this call needs more scratch than the library's fixed area holds "
                                           "(bd_noalloc_scratch_bytes); use bd_decode with a workspace";
@@ -431,6 +436,34 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     if (err != cudaSuccess) return BD_ERR_CUDA;
     if (p.defer_merge) {
         err = bd::launch_merge_parts(p, stream);
+        if (err != cudaSuccess) return BD_ERR_CUDA;
+    }
+
+    if (a->advance) {
+        // roll-over: tails that this step's token filled become the next pack block of their sequence ...
+        PackParams pk;
+        std::memset(&pk, 0, sizeof(pk));
+        pk.k = a->k_res; pk.v = a->v_res;
+        pk.k_stride_b = pk.v_stride_b = a->res_stride_b;
+        pk.k_stride_s = pk.v_stride_s = a->res_stride_s;
+        pk.k_stride_h = pk.v_stride_h = a->res_stride_h;
+        pk.k_pack = const_cast<void *>(a->k_pack); pk.k_params = const_cast<void *>(a->k_params);
+        pk.v_pack = const_cast<void *>(a->v_pack); pk.v_params = const_cast<void *>(a->v_params);
+        pk.k_pack_stride_b = a->k_pack_stride_b; pk.k_params_stride_b = a->k_params_stride_b;
+        pk.v_pack_stride_b = a->v_pack_stride_b;
+        pk.v_params_stride_b = a->v_params_stride_b; pk.v_params_stride_g = a->v_params_stride_g;
+        pk.v_params_stride_h = a->v_params_stride_h;
+        pk.b = a->b; pk.s = nb; pk.h_k = a->h_k;
+        pk.roll_res_lens = a->res_lens; pk.roll_cache_seqlens = a->cache_seqlens; pk.roll_s_cap = a->s_cap;
+        err = bd::launch_pack(pk, a->bits, a->group, a->dtype, stream);
+        if (err != cudaSuccess) return BD_ERR_CUDA;
+        // ... and every sequence's lengths move on
+        bd::AdvanceParams ad;
+        ad.cache_seqlens = const_cast<int32_t *>(a->cache_seqlens);
+        ad.res_lens = const_cast<int32_t *>(a->res_lens);
+        ad.b = a->b; ad.block_tokens = nb; ad.s_cap = a->s_cap; ad.res_cap = a->res_len;
+        ad.status = reinterpret_cast<int32_t *>(ws);
+        err = bd::launch_advance(ad, stream);
         if (err != cudaSuccess) return BD_ERR_CUDA;
     }
 

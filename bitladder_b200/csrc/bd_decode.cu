@@ -1411,6 +1411,34 @@ cudaError_t launch_decode(const DecodeParams &p, const CUtensorMap &kmap, const 
     return cudaErrorInvalidValue;
 }
 
+// ---------------------------------------------------------------------------
+// After a step that appended a token to every tail: the lengths the next step will read.  Mirrors
+// what the decode kernel did (a tail that was already full took no token) and what the roll-over
+// pack did (a tail that reached one pack block was packed, room permitting).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) bd_advance_kernel(const AdvanceParams p) {
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= p.b) return;
+    const int cap = min(kTailMax, p.res_cap);
+    int r = min(max(p.res_lens[i], 0), cap);
+    if (r < cap) r += 1;                                  // the decode kernel filed this step's token
+    if (r == p.block_tokens) {
+        const int cs = p.cache_seqlens[i];
+        if (cs >= 0 && cs % p.block_tokens == 0 && cs + p.block_tokens <= p.s_cap) {
+            p.cache_seqlens[i] = cs + p.block_tokens;
+            r = 0;
+        } else {
+            atomicExch(p.status, BD_ERR_CAPACITY);
+        }
+    }
+    p.res_lens[i] = r;
+}
+
+cudaError_t launch_advance(const AdvanceParams &p, cudaStream_t stream) {
+    bd_advance_kernel<<<(p.b + 255) / 256, 256, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_prefix(const PrefixParams &p, cudaStream_t stream) {
     bd_prefix_kernel<<<1, 256, 0, stream>>>(p);
     return cudaGetLastError();

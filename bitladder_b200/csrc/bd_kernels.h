@@ -26,6 +26,18 @@ struct PackParams {
     int32_t b, s, h_k;
     int32_t dst_token_offset;
     int32_t approx_div;           // divide like the reference built with --use_fast_math (see bd_pack.cu)
+    // Roll-over of full tails (null: plain pack).  The source rows are a sequence's tail buffer; a
+    // sequence is packed only if roll_res_lens[ib] + 1 equals one pack block (this step's token filled
+    // the tail), into the block that starts at token roll_cache_seqlens[ib] (room permitting).
+    const int32_t *roll_res_lens;
+    const int32_t *roll_cache_seqlens;
+    int32_t roll_s_cap;
+};
+
+struct AdvanceParams {
+    int32_t *cache_seqlens, *res_lens;
+    int32_t b, block_tokens, s_cap, res_cap;
+    int32_t *status;
 };
 
 // ---------------------------------------------------------------------------
@@ -232,6 +244,7 @@ struct CombinePartsParams {
 
 cudaError_t launch_pack(const PackParams &p, int bits, int group, int dtype, cudaStream_t stream);
 cudaError_t launch_prefix(const PrefixParams &p, cudaStream_t stream);
+cudaError_t launch_advance(const AdvanceParams &p, cudaStream_t stream);
 cudaError_t launch_merge_parts(const DecodeParams &p, cudaStream_t stream);
 cudaError_t launch_decode(const DecodeParams &p, const CUtensorMap &kmap, const CUtensorMap &vmap,
                           int bits, int group, cudaStream_t stream);

@@ -134,7 +134,13 @@ bd_pack_kernel(const PackParams p) {
     const int tid = threadIdx.x;
     // heads vary fastest: CTAs that run together read neighbouring 256-byte pieces of the same token rows
     const int ih = blockIdx.x, blk = blockIdx.y, ib = blockIdx.z;
-    const int dst_blk = blk + p.dst_token_offset / NB;
+    int dst_off = p.dst_token_offset;
+    if (p.roll_res_lens != nullptr) {          // roll-over: only sequences whose tail this step's token filled
+        if (p.roll_res_lens[ib] + 1 != NB) return;
+        dst_off = p.roll_cache_seqlens[ib];
+        if (dst_off < 0 || dst_off % NB != 0 || dst_off + NB > p.roll_s_cap) return;   // no room: reported by the advance kernel
+    }
+    const int dst_blk = blk + dst_off / NB;
     const uint16_t *kin = static_cast<const uint16_t *>(p.k);
     const uint16_t *vin = static_cast<const uint16_t *>(p.v);
 

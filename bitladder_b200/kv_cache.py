@@ -13,7 +13,8 @@ a branch that is not part of the project snapshot (``README.md:37``), and its fi
 
 Everything on the device goes through the two operators of this package; this file is
 host logic only.  Lengths are mirrored on the host so that a step needs no
-device-to-host synchronisation.
+device-to-host synchronisation; in the fused step (``append_and_decode``, ``decoder_step``) the
+device keeps them itself, roll-over included, and the mirror is plain arithmetic.
 """
 from __future__ import annotations
 
@@ -147,20 +148,51 @@ class PackedKVCache:
                                res_lens=self.res_lens, cache_seqlens=self.cache_seqlens,
                                seqlen_k=max(seq_hi, self.block), **kw)
 
+    def _advance_mirror(self) -> None:
+        """What the device did to the lengths in a step with ``advance``: pure host arithmetic."""
+        for ib in range(self.batch):
+            self._tail[ib] += 1
+            if self._tail[ib] == self.block and self._packed[ib] + self.block <= self.capacity:
+                self._packed[ib] += self.block
+                self._tail[ib] = 0
+
     def append_and_decode(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, softmax_scale: float,
                           **kw) -> torch.Tensor:
-        """The decoder's step in one launch: attend over everything held plus this step's token
-        ``k_new``/``v_new (batch, 1, nheads_k, head_dim)``, and leave the token in the tail."""
+        """The decoder's step: attend over everything held plus this step's token ``k_new``/``v_new
+        (batch, 1, nheads_k, head_dim)``, leave the token in the tail, and, where a tail has filled up,
+        quantize-pack it as the sequence's next block: all on the device (``advance``), no host-side
+        packing call, no synchronisation."""
         if k_new.shape != (self.batch, 1, self.nheads_k, self.head_dim) or v_new.shape != k_new.shape:
             raise RuntimeError("append_and_decode expects k_new/v_new of shape (batch, 1, nheads_k, head_dim)")
-        self._roll_full_tails()
+        self._roll_full_tails()                        # only after plain append() calls left a tail full
+        if any(p + t + 1 > self.capacity for p, t in zip(self._packed, self._tail)):
+            raise RuntimeError("cache capacity exceeded")
         seq_hi = max(self._packed) if self._packed else 0
         out = fwd_kvcache_int(q, self.k_pack, self.k_params, self.v_pack, self.v_params, None, softmax_scale,
                               "k-channel", self.group_size, self.num_bits,
                               k_res=self.k_tail, v_res=self.v_tail, res_lens=self.res_lens,
                               cache_seqlens=self.cache_seqlens, seqlen_k=max(seq_hi, self.block),
-                              k_new=k_new, v_new=v_new, **kw)
-        for ib in range(self.batch):
-            self._tail[ib] += 1
-        self.res_lens.add_(1)                          # after the step, in stream order
+                              k_new=k_new, v_new=v_new, advance=True, **kw)
+        self._advance_mirror()
         return out
+
+    def decoder_step(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, softmax_scale: float, **kw):
+        """A prepared ``DecodeStep`` that does what ``append_and_decode`` does, for a decoder loop that
+        replays a CUDA graph: ``q``, ``k_new`` and ``v_new`` are the buffers the loop refills every step;
+        ``step()`` launches the kernels and nothing else (lengths live on the device).  Call
+        ``note_steps(n)`` after n steps (or ``sync_lengths()``) before using the other methods again."""
+        from .bit_decode_interface import DecodeStep
+        self._roll_full_tails()
+        return DecodeStep(q, self.k_pack, self.k_params, self.v_pack, self.v_params, None, softmax_scale, "k-channel",
+                          self.group_size, self.num_bits, k_res=self.k_tail, v_res=self.v_tail, res_lens=self.res_lens,
+                          cache_seqlens=self.cache_seqlens, k_new=k_new, v_new=v_new, advance=True, **kw)
+
+    def note_steps(self, n: int) -> None:
+        """Tell the host mirrors that ``n`` steps of a ``decoder_step`` object have been launched."""
+        for _ in range(n):
+            self._advance_mirror()
+
+    def sync_lengths(self) -> None:
+        """Read the lengths back from the device (synchronises)."""
+        self._packed = [int(x) for x in self.cache_seqlens.tolist()]
+        self._tail = [int(x) for x in self.res_lens.tolist()]

@@ -51,6 +51,7 @@ extern "C" {
 #define BD_ERR_CUDA         -5   /* a CUDA runtime / driver call failed */
 #define BD_ERR_DEVICE       -6   /* not an sm_100 device */
 #define BD_ERR_TIMEOUT      -7   /* a bounded device-side wait ran out (see bd_read_status) */
+#define BD_ERR_CAPACITY    -10   /* status word: a tail filled up but the packed buffers have no room for its block */
 #define BD_ERR_PAGE         -9   /* status word: a block_table entry outside [0, num_pages) was met; its
                                     tokens were left out */
 #define BD_ERR_SCRATCH_LIMIT -8  /* bd_decode_noalloc: the call needs more than the fixed scratch area */
@@ -170,6 +171,17 @@ typedef struct bd_decode_args {
     int32_t num_pages;
     void *workspace;
     size_t workspace_bytes;
+    int32_t advance;          /* with k_new: after the step, advance the sequences on the device, so that a
+                                 decoder loop needs no host-side bookkeeping and the whole step can be captured
+                                 in a CUDA graph: res_lens[ib] += 1, and a tail that has reached one pack block
+                                 (NB tokens) is quantize-packed as block cache_seqlens[ib] / NB of the packed
+                                 buffers (same bytes as bd_pack on those rows), cache_seqlens[ib] += NB,
+                                 res_lens[ib] = 0.  This is the roll-over of the reference's residual scheme
+                                 (its imgs/scheme.png; residual_block_size in kernel_traits.h:76-85, not wired up
+                                 in its snapshot).  Needs cache_seqlens and res_lens (both are then WRITTEN), a tail
+                                 buffer of at least NB rows, no block_table.  Runs as two small kernels behind the
+                                 decode kernel on the same stream.  No room left for the block: BD_ERR_CAPACITY in
+                                 the status word, the tail stays full. */
     uint32_t spin_limit;      /* polls a device-side wait on a copy may take before it gives up with
                                  BD_ERR_TIMEOUT; 0 = the default (about 2^22, seconds) */
     int32_t test_starve;      /* test hook, leave 0.  1: the warps of the first CTA expect 16 bytes more
