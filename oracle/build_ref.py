@@ -39,7 +39,8 @@ from concurrent.futures import ThreadPoolExecutor
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(_HERE, "_ref")
-DEFAULT_REFERENCE = os.environ.get("BITDECODE_REFERENCE", "/root/reference")
+# the reference project's checkout: $BITDECODE_REFERENCE, else a directory `reference` beside this repository
+DEFAULT_REFERENCE = os.environ.get("BITDECODE_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
 
 GENFILES = [
     "flash_fwd_hdim128_fp16_sm80.cu",
@@ -138,7 +139,9 @@ def build(reference: str = DEFAULT_REFERENCE, variants=("fast", "ieee"), jobs: i
 
 
 def load(variant: str = "fast", relaxed: bool = True):
-    """Import a built module (needs torch imported first so that its libraries are resolved)."""
+    """Import a built module (needs torch imported first so that its libraries are resolved).  Load the
+    modules of ONE variant per process: both variants export the same module and kernel names, and with
+    both loaded the second one ran the first one's code."""
     import importlib.util
     import torch  # noqa: F401
     name = "bit_decode_cuda_sm100" if relaxed else "bit_decode_cuda"

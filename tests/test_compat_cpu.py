@@ -7,7 +7,9 @@ import sys
 import pytest
 import torch
 
-REF_IFACE = "/root/reference/bit_decode/bit_decode_interface.py"
+from oracle import build_ref
+
+REF_IFACE = os.path.join(build_ref.DEFAULT_REFERENCE, "bit_decode", "bit_decode_interface.py")
 
 
 def test_shim_exports_the_four_functions_with_the_reference_arity():
