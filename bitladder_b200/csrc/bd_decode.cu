@@ -82,7 +82,10 @@ constexpr int kMaxWarps = BD_MAX_WARPS;
 constexpr int kSmemLimit = 232448;     // 227 KB of shared memory per CTA
 constexpr float kRescaleSlack = 8.0f;  // keep a stale row max until it is exceeded by 2^8
 
-template <int BITS, int GROUP, int NQT>
+// TWO = 1: half as many warps per CTA and two CTAs per SM.  One CTA of twelve same-age warps per SM is
+// the faster arrangement wherever rows * KV heads fills the machine; with many KV heads (rows are tied
+// to whole KV heads: 32 heads leave 20 of 148 SMs without a CTA) twice as many smaller CTAs fill it better.
+template <int BITS, int GROUP, int NQT, int TWO = 0>
 struct Cfg {
     static constexpr int P = 16 / BITS;
     static constexpr int NB = 32 * P;
@@ -104,7 +107,7 @@ struct Cfg {
     // twelve warps leave a thread: eight warps (255 registers) measured 3-4 % faster at 2 bits
     // (the same holds for group 32, with four parameter sets per block)
     static constexpr int CAP = (NQT == 1 && BITS == 4 && GROUP >= 64) ? kMaxWarps : (kMaxWarps < 8 ? kMaxWarps : 8);
-    static constexpr int WARPS = FIT < CAP ? FIT : CAP;
+    static constexpr int WARPS = (FIT < CAP ? FIT : CAP) / (TWO ? 2 : 1);
     static constexpr int THREADS = WARPS * 32;
     static constexpr size_t OFF_PRM = size_t(WARPS) * 2 * CODE_BYTES;
     static constexpr size_t OFF_BAR = OFF_PRM + size_t(WARPS) * 2 * PRM_BYTES;
@@ -282,11 +285,11 @@ struct BlockCursor {
     }
 };
 
-template <int BITS, int GROUP, int NQT>
-__global__ void __launch_bounds__(Cfg<BITS, GROUP, NQT>::THREADS, Cfg<BITS, GROUP, NQT>::CTAS_PER_SM)
+template <int BITS, int GROUP, int NQT, int TWO>
+__global__ void __launch_bounds__(Cfg<BITS, GROUP, NQT, TWO>::THREADS, Cfg<BITS, GROUP, NQT, TWO>::CTAS_PER_SM)
 bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                  const __grid_constant__ CUtensorMap vmap) {
-    using C = Cfg<BITS, GROUP, NQT>;
+    using C = Cfg<BITS, GROUP, NQT, TWO>;
     constexpr int P = C::P, NB = C::NB, NGK = C::NGK, FPG = C::FPG, NGD = C::NGD, FPGV = C::FPGV;
     constexpr int DP = C::DP, RUNS = C::RUNS, PRM = C::PRM_BYTES, NACC = C::NACC, NZ = C::NZ;
     constexpr int kWarps = C::WARPS;
@@ -1374,11 +1377,11 @@ __global__ void __launch_bounds__(256) bd_prefix_kernel(const PrefixParams p) {
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
-template <int BITS, int GROUP, int NQT>
+template <int BITS, int GROUP, int NQT, int TWO>
 static cudaError_t launch_t(const DecodeParams &p, const CUtensorMap &kmap, const CUtensorMap &vmap,
                             cudaStream_t stream) {
-    using C = Cfg<BITS, GROUP, NQT>;
-    auto kern = bd_decode_kernel<BITS, GROUP, NQT>;
+    using C = Cfg<BITS, GROUP, NQT, TWO>;
+    auto kern = bd_decode_kernel<BITS, GROUP, NQT, TWO>;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
@@ -1396,8 +1399,13 @@ static cudaError_t launch_t(const DecodeParams &p, const CUtensorMap &kmap, cons
 template <int BITS, int GROUP>
 static cudaError_t launch_bg(const DecodeParams &p, const CUtensorMap &kmap, const CUtensorMap &vmap,
                              cudaStream_t stream) {
-    if (p.gq <= 8) return launch_t<BITS, GROUP, 1>(p, kmap, vmap, stream);
-    return launch_t<BITS, GROUP, 2>(p, kmap, vmap, stream);
+    if (p.gq <= 8) {
+        if constexpr (BITS == 4 && GROUP >= 64) {
+            if (p.two_ctas) return launch_t<BITS, GROUP, 1, 1>(p, kmap, vmap, stream);
+        }
+        return launch_t<BITS, GROUP, 1, 0>(p, kmap, vmap, stream);
+    }
+    return launch_t<BITS, GROUP, 2, 0>(p, kmap, vmap, stream);
 }
 
 cudaError_t launch_decode(const DecodeParams &p, const CUtensorMap &kmap, const CUtensorMap &vmap,
@@ -1446,6 +1454,8 @@ cudaError_t launch_prefix(const PrefixParams &p, cudaStream_t stream) {
 
 #define BD_CFG_PICK(FIELD)                                                                              \
     const int nqt = gq <= 8 ? 1 : 2;                                                                   \
+    if (two && decode_two_ctas_built(bits, group, gq))                                                 \
+        return group == 128 ? Cfg<4, 128, 1, 1>::FIELD : Cfg<4, 64, 1, 1>::FIELD;                       \
     if (bits == 4 && group == 128) return nqt == 1 ? Cfg<4, 128, 1>::FIELD : Cfg<4, 128, 2>::FIELD;     \
     if (bits == 4 && group == 64) return nqt == 1 ? Cfg<4, 64, 1>::FIELD : Cfg<4, 64, 2>::FIELD;        \
     if (bits == 2 && group == 128) return nqt == 1 ? Cfg<2, 128, 1>::FIELD : Cfg<2, 128, 2>::FIELD;     \
@@ -1453,26 +1463,22 @@ cudaError_t launch_prefix(const PrefixParams &p, cudaStream_t stream) {
     if (bits == 4 && group == 32) return nqt == 1 ? Cfg<4, 32, 1>::FIELD : Cfg<4, 32, 2>::FIELD;        \
     if (bits == 2 && group == 32) return nqt == 1 ? Cfg<2, 32, 1>::FIELD : Cfg<2, 32, 2>::FIELD;
 
+// Whether the two-CTAs-per-SM variant exists for this configuration (4-bit, group 64 / 128, up to 8
+// query heads per KV head: the variants that otherwise run twelve warps per CTA).
+bool decode_two_ctas_built(int bits, int group, int gq) { return bits == 4 && group >= 64 && gq <= 8; }
 // Streaming warps per CTA of the kernel that serves this configuration.
-int decode_warps(int bits, int group, int gq) {
+int decode_warps(int bits, int group, int gq, int two) {
     BD_CFG_PICK(WARPS)
     return 1;
 }
 // Floats of one warp's deposit (its partial of a segment).
-int decode_deposit_floats(int bits, int group, int gq) {
+int decode_deposit_floats(int bits, int group, int gq, int two) {
     BD_CFG_PICK(DEPOSIT_FLOATS)
     return 0;
 }
-
-int decode_ctas_per_sm(int bits, int group, int gq) {
-    const int nqt = gq <= 8 ? 1 : 2;
-    if (bits == 4 && group == 128) return nqt == 1 ? Cfg<4, 128, 1>::CTAS_PER_SM : Cfg<4, 128, 2>::CTAS_PER_SM;
-    if (bits == 4 && group == 64) return nqt == 1 ? Cfg<4, 64, 1>::CTAS_PER_SM : Cfg<4, 64, 2>::CTAS_PER_SM;
-    if (bits == 2 && group == 128) return nqt == 1 ? Cfg<2, 128, 1>::CTAS_PER_SM : Cfg<2, 128, 2>::CTAS_PER_SM;
-    if (bits == 2 && group == 64) return nqt == 1 ? Cfg<2, 64, 1>::CTAS_PER_SM : Cfg<2, 64, 2>::CTAS_PER_SM;
-    if (bits == 4 && group == 32) return nqt == 1 ? Cfg<4, 32, 1>::CTAS_PER_SM : Cfg<4, 32, 2>::CTAS_PER_SM;
-    if (bits == 2 && group == 32) return nqt == 1 ? Cfg<2, 32, 1>::CTAS_PER_SM : Cfg<2, 32, 2>::CTAS_PER_SM;
-    return 2;
+int decode_ctas_per_sm(int bits, int group, int gq, int two) {
+    BD_CFG_PICK(CTAS_PER_SM)
+    return 1;
 }
 
 }  // namespace bd

@@ -219,6 +219,7 @@ struct DecodeParams {
     int64_t out_stride_b, out_stride_h;
     int32_t out_dtype;
     int32_t defer_merge;          // the parts of a sequence are merged by bd_merge_parts_kernel, launched next
+    int32_t two_ctas;             // launch the variant with two smaller CTAs per SM
     uint32_t spin_limit;          // polls a wait on a copy may take before the warp gives up
     int32_t test_starve;          // test hook: the warps of CTA 0 expect 16 bytes more than their first copy brings
     int32_t *status;
@@ -248,9 +249,11 @@ cudaError_t launch_advance(const AdvanceParams &p, cudaStream_t stream);
 cudaError_t launch_merge_parts(const DecodeParams &p, cudaStream_t stream);
 cudaError_t launch_decode(const DecodeParams &p, const CUtensorMap &kmap, const CUtensorMap &vmap,
                           int bits, int group, cudaStream_t stream);
-int decode_ctas_per_sm(int bits, int group, int gq);
-int decode_warps(int bits, int group, int gq);
-int decode_deposit_floats(int bits, int group, int gq);
+// `two`: the variant with half as many warps per CTA and two CTAs per SM (see Cfg in bd_decode.cu)
+bool decode_two_ctas_built(int bits, int group, int gq);
+int decode_ctas_per_sm(int bits, int group, int gq, int two);
+int decode_warps(int bits, int group, int gq, int two);
+int decode_deposit_floats(int bits, int group, int gq, int two);
 cudaError_t launch_combine_parts(const CombinePartsParams &p, cudaStream_t stream);
 
 }  // namespace bd
