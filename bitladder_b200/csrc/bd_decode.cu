@@ -103,10 +103,11 @@ struct Cfg {
     // per warp: one K tile and one V tile, then their scales/zeros
     static constexpr int WARP_BYTES = 2 * CODE_BYTES + 2 * PRM_BYTES + 16;
     static constexpr int FIT = (kSmemLimit - 32) / (WARP_BYTES + 32);
-    // eight fields per word (2 bits) and two query tiles both need more than the 168 registers
-    // twelve warps leave a thread: eight warps (255 registers) measured 3-4 % faster at 2 bits
-    // (the same holds for group 32, with four parameter sets per block)
-    static constexpr int CAP = (NQT == 1 && BITS == 4 && GROUP >= 64) ? kMaxWarps : (kMaxWarps < 8 ? kMaxWarps : 8);
+    // Twelve warps leave a thread 168 registers (three warps per scheduler; so do 9 to 11).  One query tile
+    // fits them at 4 bits and, taking a block unit by unit, at 2 bits (C3 48.4 -> 44.6 us, C5a 2-bit 349 ->
+    // 340 us against eight warps with 255 registers); two query tiles and group 32 (four parameter sets per
+    // block) need more and run eight warps.
+    static constexpr int CAP = (NQT == 1 && GROUP >= 64) ? kMaxWarps : (kMaxWarps < 8 ? kMaxWarps : 8);
     static constexpr int WARPS = (FIT < CAP ? FIT : CAP) / (TWO ? 2 : 1);
     static constexpr int THREADS = WARPS * 32;
     static constexpr size_t OFF_PRM = size_t(WARPS) * 2 * CODE_BYTES;
@@ -117,7 +118,7 @@ struct Cfg {
     static constexpr int DEPOSIT_FLOATS = NACC * 32;                        // one warp's share of a segment
     static_assert(DEPOSIT_FLOATS * 4 <= 2 * CODE_BYTES, "a deposit fits the warp's own tile slots");
     static constexpr int CTAS_PER_SM = (SMEM + 1024) * 3 <= 233472 ? 3 : ((SMEM + 1024) * 2 <= 233472 ? 2 : 1);
-    static_assert(WARPS >= 1 && WARPS <= 32, "one mask bit per warp");
+    static_assert(WARPS >= 1 && WARPS < 16, "one mask bit per warp; the segment notes use lanes 0..WARPS and 16, 17");
     static_assert(SMEM <= size_t(kSmemLimit), "shared memory");
 };
 
@@ -274,8 +275,9 @@ struct BlockCursor {
         }
         return false;
     }
-    __device__ __forceinline__ void init(const Partition &pt, int row, const int32_t *cs, int32_t s_, int32_t nb) {
-        walk.init(pt, row);
+    // starts from a walk that stands at the beginning of the warp's row
+    __device__ __forceinline__ void init(const SegWalk &start, const int32_t *cs, int32_t s_, int32_t nb) {
+        walk = start;
         cache_seqlens = cs; s = s_; block_tokens = nb;
         valid = seek();
     }
@@ -333,7 +335,6 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
         tma_prefetch_desc(&kmap);
         tma_prefetch_desc(&vmap);
     }
-    __syncthreads();
     // The warps are the rows of the partition with kWarps times the CTA rows.
     Partition wpart = p.part;
     wpart.R = p.part.R * kWarps;
@@ -379,13 +380,17 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     };
 
     // ---- prologue: first block of this warp ------------------------------------
+    SegWalk walk;                   // this warp's segments, in order
+    walk.init(wpart, wrow);
     BlockCursor ld;                 // next block to copy into this warp's tiles
-    ld.init(wpart, wrow, p.cache_seqlens, p.s, NB);
+    ld.init(walk, p.cache_seqlens, p.s, NB);
     if (ld.valid && lane == 0) {
         issue_k(ld.sg.ib, ld.u);
         issue_v(ld.sg.ib, ld.u);
     }
+    if (ld.valid) { BD_TRACE_MARK(20); }
     if (ld.valid) ld.advance();
+    __syncthreads();          // every warp's flags and barriers are set up (its own first copies are already on their way)
 
     // thread-constant shared-memory offsets
     // K tile: two halves of 64 channels, each [32 pack rows][128 B] with the 128-byte
@@ -410,8 +415,6 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     uint32_t phase = 0;    // parity of both barriers: one completion each per consumed block
     bool aborted = false;
 
-    SegWalk walk;
-    walk.init(wpart, wrow);
     Segment sg;
     while (walk.next(sg)) {
         const int ib = sg.ib;
@@ -457,35 +460,6 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             *reinterpret_cast<uint2 *>(static_cast<uint16_t *>(p.v_res_out) + dst) = vw;
         }
 
-        // Which warps of this CTA share the sequence, which of them goes on with another sequence
-        // afterwards, and how many CTA rows hold a part of it: worked out now, while the first copies
-        // are in flight, and kept in shared memory (not in registers across the streaming loop).
-        {
-            const int64_t Tw = wpart.total();
-            const int64_t seq_first = wpart.first(ib), seq_end = seq_first + wpart.count(ib);
-            uint32_t share_mask = 0;
-            int goes_on = -1;
-            int64_t lo = wpart.row_begin(int64_t(row) * kWarps, Tw);
-#pragma unroll 1
-            for (int w = 0; w < kWarps; ++w) {
-                const int64_t hi = wpart.row_begin(int64_t(row) * kWarps + w + 1, Tw);
-                if (max(lo, seq_first) < min(hi, seq_end)) {
-                    share_mask |= 1u << w;
-                    if (hi > seq_end) goes_on = w;
-                }
-                lo = hi;
-            }
-            const PartRange pr = part_range(p.part, ib);
-            int nparts = pr.c1 - pr.c0 + 1;
-            if (!pr.dense) {
-                nparts = 0;
-                for (int c = pr.c0; c <= pr.c1; ++c) nparts += row_has_part(p.part, ib, c) ? 1 : 0;
-            }
-            if (lane == 0)
-                *note = make_int4(int(share_mask), (goes_on + 1) | ((pr.c1 - pr.c0 + 1) << 8), pr.c0, (nparts << 1) | (pr.dense ? 1 : 0));
-            __syncwarp();
-        }
-
         // Query rows as B fragments: thread (g, l) holds q[row g][32a + 8l .. +7], a = 0..3.
         uint32_t qr[NQT][4][4];
 #pragma unroll
@@ -505,6 +479,41 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                 }
                 qr[nq][a][0] = v.x; qr[nq][a][1] = v.y; qr[nq][a][2] = v.z; qr[nq][a][3] = v.w;
             }
+        }
+
+        // Which warps of this CTA share the sequence, which of them goes on with another sequence
+        // afterwards, and how many CTA rows hold a part of it: worked out now, while the first copies
+        // and the query loads are in flight, and kept in shared memory (not in registers across the
+        // streaming loop).  One division per lane: lanes 0..kWarps the first unit of each warp's range,
+        // lanes 16 and 17 the first and the last CTA row that holds a part of the sequence.
+        {
+            const int64_t Tw = wpart.total();
+            const int64_t seq_first = wpart.first(ib), seq_n = wpart.count(ib), seq_end = seq_first + seq_n;
+            int64_t num = (int64_t(row) * kWarps + lane) * Tw, den = wpart.R;
+            if (lane >= 16) {
+                num = (seq_first + (lane == 16 ? 1 : seq_n)) * p.part.R - 1;
+                den = Tw;
+            }
+            const int64_t quo = div_nn(num, den > 0 ? den : 1);
+            const int64_t lo = quo, hi = __shfl_down_sync(0xffffffffu, quo, 1);
+            const bool shares = lane < kWarps && max(lo, seq_first) < min(hi, seq_end);
+            const uint32_t share_mask = __ballot_sync(0xffffffffu, shares);
+            const uint32_t on_mask = __ballot_sync(0xffffffffu, shares && hi > seq_end);
+            const int goes_on = on_mask ? 31 - __clz(on_mask) : -1;
+            PartRange pr{0, -1, true};
+            if (seq_n > 0 && Tw > 0) {
+                pr.c0 = int(__shfl_sync(0xffffffffu, quo, 16));
+                pr.c1 = int(__shfl_sync(0xffffffffu, quo, 17));
+                pr.dense = Tw >= p.part.R;
+            }
+            int nparts = pr.c1 - pr.c0 + 1;
+            if (!pr.dense) {
+                nparts = 0;
+                for (int c = pr.c0; c <= pr.c1; ++c) nparts += row_has_part(p.part, ib, c) ? 1 : 0;
+            }
+            if (lane == 0)
+                *note = make_int4(int(share_mask), (goes_on + 1) | ((pr.c1 - pr.c0 + 1) << 8), pr.c0, (nparts << 1) | (pr.dense ? 1 : 0));
+            __syncwarp();
         }
 
         float O[NQT][8][4];
@@ -621,6 +630,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
         }
 
         for (int blk = blk0; blk < blk1 && !aborted; ++blk) {
+            if (phase == 0 && blk == blk0) { BD_TRACE_MARK(21); }
             int seqlen_blk = seqlen;              // tokens of the sequence this block may use
             if (p.block_table != nullptr) {
                 int pib = ib, pblk = blk;
@@ -633,6 +643,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 
             // ------------------------------------------------------------ K phase
             if (!mbar_wait_bounded(kbar, phase, p.spin_limit)) { aborted = true; break; }
+            if (phase == 0 && blk == blk0) { BD_TRACE_MARK(22); }
 
             // q . zero per token group (rows of the A operand all equal the zero vector)
             float Zc[NGK][NQT][2];
@@ -665,14 +676,87 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                     }
             }
 
+            // V phase of one unit (16 token slices of the V tile): O += P V for the unit's probabilities.
+            auto v_unit = [&](const int u, const uint32_t (&pbu)[P][NQT][2]) {
+#pragma unroll
+                for (int j = 0; j < P; ++j) {
+                    const int T0 = 16 * u + 32 * j;                       // first token of this k-slice
+                    const int r0 = T0 + 2 * l;                            // tokens of fragment register 0
+                    uint32_t sc0[NGD], sc1[NGD], ze0[NGD], ze1[NGD];    // tokens r0, r0+1 and r0+8, r0+9 (same run)
+#pragma unroll
+                    for (int gd = 0; gd < NGD; ++gd) {
+                        const uint32_t b0 = vprm + vprm_off<BITS, GROUP>(gd, r0, 0), b1 = vprm + vprm_off<BITS, GROUP>(gd, r0, 1);
+                        sc0[gd] = lds32(b0);
+                        sc1[gd] = lds32(b1);
+                        ze0[gd] = lds32(b0 + 256);
+                        ze1[gd] = lds32(b1 + 256);
+                    }
+                    if (need_mask) {          // params of tokens past the end may be uninitialised
+                        const int tok = blk * NB + r0;
+                        const uint32_t k0 = (tok < seqlen_blk ? 0x0000ffffu : 0u) | (tok + 1 < seqlen_blk ? 0xffff0000u : 0u);
+                        const uint32_t k1 = (tok + 8 < seqlen_blk ? 0x0000ffffu : 0u) | (tok + 9 < seqlen_blk ? 0xffff0000u : 0u);
+#pragma unroll
+                        for (int gd = 0; gd < NGD; ++gd) { sc0[gd] &= k0; ze0[gd] &= k0; sc1[gd] &= k1; ze1[gd] &= k1; }
+                    }
+                    uint32_t pv[NGD][NQT][2];
+#pragma unroll
+                    for (int nq = 0; nq < NQT; ++nq) {
+                        // rows 0-7: sum_t p_t * zero_t of dim group 0; rows 8-15: the same for dim
+                        // group 1 or, with a single dim group, sum_t p_t (the softmax denominator,
+                        // from the same rounded probabilities the numerator uses)
+                        constexpr uint32_t kOnes = 0x3c003c00u;
+#pragma unroll
+                        for (int z = 0; z < NZ; ++z)
+                            mma_f16(ZS[nq][z], ze0[2 * z], NGD > 1 ? ze0[NGD > 1 ? 2 * z + 1 : 0] : kOnes, ze1[2 * z],
+                                    NGD > 1 ? ze1[NGD > 1 ? 2 * z + 1 : 0] : kOnes, pbu[j][nq][0], pbu[j][nq][1]);
+#pragma unroll
+                        for (int gd = 0; gd < NGD; ++gd) {
+                            pv[gd][nq][0] = hmul2_u32(pbu[j][nq][0], sc0[gd]);
+                            pv[gd][nq][1] = hmul2_u32(pbu[j][nq][1], sc1[gd]);
+                        }
+                    }
+                    constexpr int NCB = (BITS == 4) ? 2 : 1;              // ldmatrix.x4 per k-slice
+#pragma unroll
+                    for (int cb = 0; cb < NCB; ++cb) {
+                        uint32_t r0w, r1w, r2w, r3w;
+                        ldsm_x4_trans(vcode + T0 * (DP * 2) + v_off[cb], r0w, r1w, r2w, r3w);
+                        const uint32_t s0w = aux_word<BITS>(r0w), s1w = aux_word<BITS>(r1w), s2w = aux_word<BITS>(r2w), s3w = aux_word<BITS>(r3w);
+                        auto do_vfield = [&](auto jc) {
+                            constexpr int JV = decltype(jc)::value;
+                            constexpr int gd = JV / FPGV;
+                            const int mt = (BITS == 4) ? (cb * 4 + JV) : JV;
+#pragma unroll
+                            for (int nq = 0; nq < NQT; ++nq)
+                                mma_f16(O[nq][mt], field<BITS, JV, kFieldPairs<BITS, GROUP>>(r0w, s0w),
+                                        field<BITS, JV, kFieldPairs<BITS, GROUP>>(r1w, s1w),
+                                        field<BITS, JV, kFieldPairs<BITS, GROUP>>(r2w, s2w),
+                                        field<BITS, JV, kFieldPairs<BITS, GROUP>>(r3w, s3w),
+                                        pv[gd][nq][0], pv[gd][nq][1]);
+                        };
+                        do_vfield(std::integral_constant<int, 0>{});
+                        do_vfield(std::integral_constant<int, 1>{});
+                        do_vfield(std::integral_constant<int, 2>{});
+                        do_vfield(std::integral_constant<int, 3>{});
+                        if constexpr (P == 8) {
+                            do_vfield(std::integral_constant<int, 4>{});
+                            do_vfield(std::integral_constant<int, 5>{});
+                            do_vfield(std::integral_constant<int, 6>{});
+                            do_vfield(std::integral_constant<int, 7>{});
+                        }
+                    }
+                }
+            };
+
             // Units (16 pack rows) that share one softmax step: both of a 4-bit block (one
             // step per block), one of a 2-bit block (its 8 fields fill the registers).
             constexpr int UG = (P == 4) ? 2 : 1;
-            uint32_t Pb[2][P][NQT][2];      // probabilities as B fragments (fp16), per unit and field
-            // One group at 4 bits.  At 2 bits two groups: with G=64 they run through the same
-            // (rolled) code, which measured 3 % faster there (the block body is about 50 KB and
-            // instruction fetch is that kernel's largest stall) and 2.5 % slower with G=128.
-            constexpr int kGroupUnroll = (UG == 1 && GROUP == 64) ? 1 : 2;
+            // With one unit per softmax step (2 bits) a unit goes all the way, K phase, softmax step, V
+            // phase, before the next one starts: one unit's probabilities are alive at a time and the
+            // whole block body is one rolled loop over the two units (half the instruction bytes).
+            constexpr bool kUnitByUnit = (UG == 1);
+            uint32_t Pb[kUnitByUnit ? 1 : 2][P][NQT][2];      // probabilities as B fragments (fp16), per unit and field
+            // One group at 4 bits; at 2 bits the two units run through the same (rolled) code.
+            constexpr int kGroupUnroll = kUnitByUnit ? 1 : 2;
 #pragma unroll kGroupUnroll
             for (int ug = 0; ug < 2 / UG; ++ug) {
                 float S[UG][P][NQT][4];
@@ -776,36 +860,33 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                                 }
                     }
                     float f[2];
-                    if (softmax_step<UG * P, (NGD > 1), NZ>(t, m_run[nq], l_run[nq], O[nq], ZS[nq], f) && ug > 0) {
-                        // The earlier units' probabilities are still waiting (as B fragments,
-                        // column = g) for the V phase: bring them to the new maximum too.
-                        const float f0 = __shfl_sync(0xffffffffu, f[0], g >> 1);
-                        const float f1 = __shfl_sync(0xffffffffu, f[1], g >> 1);
-                        const float fq = (g & 1) ? f1 : f0;
-                        const uint32_t fh = pack_f16x2(fq, fq);
-                        // (only reached with one unit per group: the earlier unit is unit 0)
-#pragma unroll
-                        for (int j = 0; j < P; ++j) {
-                            Pb[0][j][nq][0] = hmul2_u32(Pb[0][j][nq][0], fh);
-                            Pb[0][j][nq][1] = hmul2_u32(Pb[0][j][nq][1], fh);
-                        }
-                    }
+                    softmax_step<UG * P, (NGD > 1), NZ>(t, m_run[nq], l_run[nq], O[nq], ZS[nq], f);
 #pragma unroll
                     for (int uu = 0; uu < UG; ++uu)
 #pragma unroll
                         for (int j = 0; j < P; ++j) {
-                            const uint32_t p0 = movmatrix_trans(pack_f16x2(t[uu * P + j][0], t[uu * P + j][1]));
-                            const uint32_t p1 = movmatrix_trans(pack_f16x2(t[uu * P + j][2], t[uu * P + j][3]));
-                            if constexpr (UG == 2) {
-                                Pb[uu][j][nq][0] = p0; Pb[uu][j][nq][1] = p1;
-                            } else if (ug == 0) {          // a runtime index when the group loop is rolled
-                                Pb[0][j][nq][0] = p0; Pb[0][j][nq][1] = p1;
-                            } else {
-                                Pb[1][j][nq][0] = p0; Pb[1][j][nq][1] = p1;
-                            }
+                            Pb[uu][j][nq][0] = movmatrix_trans(pack_f16x2(t[uu * P + j][0], t[uu * P + j][1]));
+                            Pb[uu][j][nq][1] = movmatrix_trans(pack_f16x2(t[uu * P + j][2], t[uu * P + j][3]));
                         }
                 }
+                if constexpr (kUnitByUnit) {
+                    if (ug == 1) {
+                        // K tile consumed: refill it with the next block's K
+                        __syncwarp();
+                        if (lane == 0 && ld.valid) {
+                            fence_proxy_async();
+                            issue_k(ld.sg.ib, ld.u);
+                        }
+                    } else if (!mbar_wait_bounded(vbar, phase, p.spin_limit)) {
+                        aborted = true;
+                        break;
+                    }
+                    v_unit(ug, Pb[0]);
+                }
             }
+            if constexpr (kUnitByUnit) {
+                if (aborted) break;
+            } else {
             // K tile consumed: refill it with the next block's K while V is processed
             __syncwarp();
             if (lane == 0 && ld.valid) {
@@ -814,7 +895,9 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             }
 
             // ------------------------------------------------------------ V phase
+            if (phase == 0 && blk == blk0) { BD_TRACE_MARK(23); }
             if (!mbar_wait_bounded(vbar, phase, p.spin_limit)) { aborted = true; break; }
+            if (phase == 0 && blk == blk0) { BD_TRACE_MARK(24); }
             // The two units run through the same code (a rolled loop: half the instruction bytes of
             // the largest part of the block's code); their probabilities are picked with selects.
 #pragma unroll 1
@@ -827,73 +910,8 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                         pbu[j][nq][0] = u ? Pb[1][j][nq][0] : Pb[0][j][nq][0];
                         pbu[j][nq][1] = u ? Pb[1][j][nq][1] : Pb[0][j][nq][1];
                     }
-#pragma unroll
-                for (int j = 0; j < P; ++j) {
-                    const int T0 = 16 * u + 32 * j;                       // first token of this k-slice
-                    const int r0 = T0 + 2 * l;                            // tokens of fragment register 0
-                    uint32_t sc0[NGD], sc1[NGD], ze0[NGD], ze1[NGD];    // tokens r0, r0+1 and r0+8, r0+9 (same run)
-#pragma unroll
-                    for (int gd = 0; gd < NGD; ++gd) {
-                        const uint32_t b0 = vprm + vprm_off<BITS, GROUP>(gd, r0, 0), b1 = vprm + vprm_off<BITS, GROUP>(gd, r0, 1);
-                        sc0[gd] = lds32(b0);
-                        sc1[gd] = lds32(b1);
-                        ze0[gd] = lds32(b0 + 256);
-                        ze1[gd] = lds32(b1 + 256);
-                    }
-                    if (need_mask) {          // params of tokens past the end may be uninitialised
-                        const int tok = blk * NB + r0;
-                        const uint32_t k0 = (tok < seqlen_blk ? 0x0000ffffu : 0u) | (tok + 1 < seqlen_blk ? 0xffff0000u : 0u);
-                        const uint32_t k1 = (tok + 8 < seqlen_blk ? 0x0000ffffu : 0u) | (tok + 9 < seqlen_blk ? 0xffff0000u : 0u);
-#pragma unroll
-                        for (int gd = 0; gd < NGD; ++gd) { sc0[gd] &= k0; ze0[gd] &= k0; sc1[gd] &= k1; ze1[gd] &= k1; }
-                    }
-                    uint32_t pv[NGD][NQT][2];
-#pragma unroll
-                    for (int nq = 0; nq < NQT; ++nq) {
-                        // rows 0-7: sum_t p_t * zero_t of dim group 0; rows 8-15: the same for dim
-                        // group 1 or, with a single dim group, sum_t p_t (the softmax denominator,
-                        // from the same rounded probabilities the numerator uses)
-                        constexpr uint32_t kOnes = 0x3c003c00u;
-#pragma unroll
-                        for (int z = 0; z < NZ; ++z)
-                            mma_f16(ZS[nq][z], ze0[2 * z], NGD > 1 ? ze0[NGD > 1 ? 2 * z + 1 : 0] : kOnes, ze1[2 * z],
-                                    NGD > 1 ? ze1[NGD > 1 ? 2 * z + 1 : 0] : kOnes, pbu[j][nq][0], pbu[j][nq][1]);
-#pragma unroll
-                        for (int gd = 0; gd < NGD; ++gd) {
-                            pv[gd][nq][0] = hmul2_u32(pbu[j][nq][0], sc0[gd]);
-                            pv[gd][nq][1] = hmul2_u32(pbu[j][nq][1], sc1[gd]);
-                        }
-                    }
-                    constexpr int NCB = (BITS == 4) ? 2 : 1;              // ldmatrix.x4 per k-slice
-#pragma unroll
-                    for (int cb = 0; cb < NCB; ++cb) {
-                        uint32_t r0w, r1w, r2w, r3w;
-                        ldsm_x4_trans(vcode + T0 * (DP * 2) + v_off[cb], r0w, r1w, r2w, r3w);
-                        const uint32_t s0w = aux_word<BITS>(r0w), s1w = aux_word<BITS>(r1w), s2w = aux_word<BITS>(r2w), s3w = aux_word<BITS>(r3w);
-                        auto do_vfield = [&](auto jc) {
-                            constexpr int JV = decltype(jc)::value;
-                            constexpr int gd = JV / FPGV;
-                            const int mt = (BITS == 4) ? (cb * 4 + JV) : JV;
-#pragma unroll
-                            for (int nq = 0; nq < NQT; ++nq)
-                                mma_f16(O[nq][mt], field<BITS, JV, kFieldPairs<BITS, GROUP>>(r0w, s0w),
-                                        field<BITS, JV, kFieldPairs<BITS, GROUP>>(r1w, s1w),
-                                        field<BITS, JV, kFieldPairs<BITS, GROUP>>(r2w, s2w),
-                                        field<BITS, JV, kFieldPairs<BITS, GROUP>>(r3w, s3w),
-                                        pv[gd][nq][0], pv[gd][nq][1]);
-                        };
-                        do_vfield(std::integral_constant<int, 0>{});
-                        do_vfield(std::integral_constant<int, 1>{});
-                        do_vfield(std::integral_constant<int, 2>{});
-                        do_vfield(std::integral_constant<int, 3>{});
-                        if constexpr (P == 8) {
-                            do_vfield(std::integral_constant<int, 4>{});
-                            do_vfield(std::integral_constant<int, 5>{});
-                            do_vfield(std::integral_constant<int, 6>{});
-                            do_vfield(std::integral_constant<int, 7>{});
-                        }
-                    }
-                }
+                v_unit(u, pbu);
+            }
             }
             // V tile consumed: refill it, then move the load cursor on
             __syncwarp();
