@@ -507,7 +507,9 @@ def measure(B, name, w, args, device, rank, world, dist, steps, warmup, want_e2e
 
     sm = torch.cuda.get_device_properties(device).multi_processor_count
     rows = args.num_splits * sh.b if args.num_splits > 0 else B.plan_splits(sh.b, sh.h_k, sh.s, w["bits"], sm)
-    launches = 1 + (1 if w["ragged"] else 0) + (1 if rows > 4 * sh.b else 0) + (exchange["launches"] if exchange else 0)
+    fused_exchange = bool(exchange and exchange.get("merges_local_parts"))      # no parts-merge kernel then
+    launches = (1 + (1 if w["ragged"] else 0) + (1 if rows > 4 * sh.b and not fused_exchange else 0) +
+                (exchange["launches"] if exchange else 0))
     peak, peak_src = measured_peak_gbs()
     achieved = local_bytes / (ms_per_step * 1e-3) / 1e9        # this rank's bytes over the step time (slowest rank's time)
     ratio = NCU_TRAFFIC_RATIO.get(name if world == 1 else "")

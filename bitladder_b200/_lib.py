@@ -23,7 +23,7 @@ EXPORTS = (
     "bd_partition_segments", "bd_partition_parts",
     "bd_decode_noalloc", "bd_noalloc_scratch_bytes",
     "bd_exchange_area_bytes", "bd_peer_alloc", "bd_peer_free", "bd_peer_export", "bd_peer_open", "bd_peer_close",
-    "bd_exchange_combine", "bd_exchange_put", "bd_exchange_state",
+    "bd_exchange_combine", "bd_exchange_put", "bd_exchange_state", "bd_decode_exchange",
 )
 
 
@@ -137,10 +137,11 @@ def load():
     lib.bd_peer_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
     lib.bd_peer_close.argtypes = [C.c_void_p]
     lib.bd_exchange_combine.argtypes = [C.POINTER(ExchangeArgs), C.c_void_p]
+    lib.bd_decode_exchange.argtypes = [C.POINTER(DecodeArgs), C.POINTER(ExchangeArgs), C.c_void_p]
     lib.bd_exchange_put.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.bd_exchange_state.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32)]
     for name in ("bd_peer_alloc", "bd_peer_free", "bd_peer_export", "bd_peer_open", "bd_peer_close",
-                 "bd_exchange_combine", "bd_exchange_put", "bd_exchange_state"):
+                 "bd_exchange_combine", "bd_exchange_put", "bd_exchange_state", "bd_decode_exchange"):
         getattr(lib, name).restype = C.c_int
     lib.bd_strerror.argtypes = [C.c_int]
     lib.bd_strerror.restype = C.c_char_p

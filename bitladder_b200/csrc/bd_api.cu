@@ -350,9 +350,17 @@ size_t bd_decode_workspace_bytes(const bd_decode_args *a) {
     return plan.total_bytes;
 }
 
-int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
+// The decode step; with `x` the step of one rank of a sequence split: every segment leaves its part in
+// the workspace and the exchange kernel merges them, sends the rows to the peers and merges theirs.
+static int decode_step(const bd_decode_args *a, const bd_exchange_args *x, bd_stream_t stream_) {
     int rc = check_decode_args(a);
     if (rc != BD_OK) return rc;
+    bd::ExchangeParams xp;
+    if (x) {
+        rc = bd::fill_exchange_params(x, xp);
+        if (rc != BD_OK) return rc;
+        if (x->rows != int64_t(a->b) * a->h) return BD_ERR_INVALID;
+    }
     DeviceInfo info;
     rc = current_device_info(info);
     if (rc != BD_OK) return rc;
@@ -444,11 +452,20 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     // More than four parts per sequence on average (few long sequences cut over all SMs): one warp
     // merging them at the end of the decode kernel would be the tail of the step; a second kernel
     // with a warp per (sequence, query head) does it in parallel.
-    p.defer_merge = plan.rows > 4 * a->b ? 1 : 0;
+    p.defer_merge = (x || plan.rows > 4 * a->b) ? 1 : 0;
+    p.leave_parts = x ? 1 : 0;
     p.two_ctas = plan.two_ctas;
     err = bd::launch_decode(p, kmap, vmap, a->bits, a->group, stream);
     if (err != cudaSuccess) return BD_ERR_CUDA;
-    if (p.defer_merge) {
+    if (x) {
+        xp.part_out = p.part_out; xp.part_lse = p.part_lse;
+        xp.out = p.out; xp.lse = p.lse;
+        xp.out_stride_b = p.out_stride_b; xp.out_stride_h = p.out_stride_h;
+        xp.h = p.h; xp.out_dtype = p.out_dtype;
+        xp.part = p.part; xp.h_k = p.h_k; xp.gq = p.gq;
+        err = bd::launch_exchange_parts(xp, stream);
+        if (err != cudaSuccess) return BD_ERR_CUDA;
+    } else if (p.defer_merge) {
         err = bd::launch_merge_parts(p, stream);
         if (err != cudaSuccess) return BD_ERR_CUDA;
     }
@@ -482,6 +499,13 @@ int bd_decode(const bd_decode_args *a, bd_stream_t stream_) {
     }
 
     return BD_OK;
+}
+
+int bd_decode(const bd_decode_args *a, bd_stream_t stream) { return decode_step(a, nullptr, stream); }
+
+int bd_decode_exchange(const bd_decode_args *a, const bd_exchange_args *x, bd_stream_t stream) {
+    if (!x) return BD_ERR_INVALID;
+    return decode_step(a, x, stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -1038,7 +1038,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
             PartRange pr;
             pr.c0 = nt.z; pr.dense = (nt.w & 1) != 0;
             pr.c1 = pr.c0 + (nt.y >> 8) - 1;
-            const bool final_here = nparts <= 1;
+            const bool final_here = nparts <= 1 && !p.leave_parts;     // (a sequence split over GPUs always leaves parts)
             const int64_t slot = (int64_t(row) + ib) * p.h_k + ih;
             // normalise in place, then one straight run of stores per destination kind
             bool row_ok[NQT][2];

@@ -12,6 +12,8 @@
 #define BD_HD __host__ __device__ __forceinline__
 #endif
 
+struct bd_exchange_args;
+
 namespace bd {
 
 struct PackParams {
@@ -218,7 +220,8 @@ struct DecodeParams {
     float *lse;                   // optional (b, h)
     int64_t out_stride_b, out_stride_h;
     int32_t out_dtype;
-    int32_t defer_merge;          // the parts of a sequence are merged by bd_merge_parts_kernel, launched next
+    int32_t defer_merge;          // the parts of a sequence are merged by a kernel launched next
+    int32_t leave_parts;          // every segment leaves a part, also where a sequence has a single one (the exchange merges)
     int32_t two_ctas;             // launch the variant with two smaller CTAs per SM
     uint32_t spin_limit;          // polls a wait on a copy may take before the warp gives up
     int32_t test_starve;          // test hook: the warps of CTA 0 expect 16 bytes more than their first copy brings
@@ -242,6 +245,26 @@ struct CombinePartsParams {
     int32_t n_parts;
     int32_t out_dtype;
 };
+
+// Exchange of a sequence split's partials between GPUs (bd_exchange.cu).
+struct ExchangeParams {
+    uint8_t *area[16];               // area of every rank as mapped into this process; area[rank] is local
+    const float *part_out;           // this rank's normalised partial (rows, 128), or the decode kernel's parts
+    const float *part_lse;
+    void *out;
+    float *lse;
+    int64_t rows;                    // b * h
+    int64_t out_stride_b, out_stride_h;
+    int32_t h;                       // rows per sequence
+    int32_t rank, world, out_dtype;
+    uint32_t spin_limit;
+    // fused with the decode step: where the decode kernel's CTAs left their parts
+    Partition part;
+    int32_t h_k, gq;
+};
+cudaError_t launch_exchange_parts(const ExchangeParams &p, cudaStream_t stream);
+// checks the exchange half of a call and fills areas, rank, world, rows and the poll limit from it
+int fill_exchange_params(const ::bd_exchange_args *a, ExchangeParams &p);
 
 cudaError_t launch_pack(const PackParams &p, int bits, int group, int dtype, cudaStream_t stream);
 cudaError_t launch_prefix(const PrefixParams &p, cudaStream_t stream);

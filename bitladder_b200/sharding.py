@@ -171,14 +171,15 @@ class PeerExchange:
 class SequenceParallelStep:
     """``decode_sequence_parallel`` prepared once for a decoder loop.
 
-    The local step is a ``DecodeStep`` that writes this rank's fp32 partial and its log-sum-exps; then
-
-    * ``exchange="peer"`` (default on GPUs): ONE kernel (``bd_exchange_combine``) stores the partial into
-      every peer's exchange area over NVLink, waits (bounded) for the peers' partials in its own area and
-      merges them.  No NCCL call on the step, nothing allocated, capturable in a CUDA graph
+    * ``exchange="peer"`` (default on GPUs): the step is ``bd_decode_exchange``: the decode kernel over this
+      rank's shard leaves its CTAs' parts in the workspace, and ONE more kernel merges them row by row,
+      stores each row into every peer's exchange area over NVLink (values and the step's epoch side by
+      side, no fence or flag), polls (bounded) for the peers' rows in its own area and merges them.
+      Two launches per step, no NCCL call, nothing allocated, capturable in a CUDA graph
       (``capturable``).  A peer that does not publish makes the kernel give up after ``spin_limit`` polls
       and leave ``BD_ERR_TIMEOUT`` in the area's status word (``check()`` raises then).
-    * ``exchange="nccl"``: one ``all_gather_into_tensor`` of ``b*h*(d+1)`` fp32 values per rank and one
+    * ``exchange="nccl"``: the local step is a ``DecodeStep`` that writes this rank's fp32 partial and its
+      log-sum-exps, then one ``all_gather_into_tensor`` of ``b*h*(d+1)`` fp32 values per rank and one
       ``bd_combine`` launch over pointers into the gathered buffer.
 
     ``step()`` returns the full result on every rank."""
@@ -199,24 +200,29 @@ class SequenceParallelStep:
         n = lse_off + (rows + 3) // 4 * 4
         dev = q.device
         self._dev = dev
-        self._local = torch.empty(n, dtype=torch.float32, device=dev)
-        self._local_step = DecodeStep(q, k_pack, k_params, v_pack, v_params, None, softmax_scale, "k-channel",
-                                      group_size, num_bits, seqlen_k=seqlen_k, k_res=k_res, v_res=v_res,
-                                      res_lens=res_lens, cache_seqlens=cache_seqlens,
-                                      out=self._local[:n_out].view(b, 1, h, d), lse=self._local[lse_off:lse_off + rows])
         self.out = torch.empty((b, 1, h, d), dtype=out_dtype or q.dtype, device=dev)
         self.kind = exchange
         if exchange == "peer":
+            # the decode step writes nothing final itself: out receives the merged result of all ranks
+            self._local_step = DecodeStep(q, k_pack, k_params, v_pack, v_params, None, softmax_scale, "k-channel",
+                                          group_size, num_bits, seqlen_k=seqlen_k, k_res=k_res, v_res=v_res,
+                                          res_lens=res_lens, cache_seqlens=cache_seqlens, out=self.out)
             self.peers = PeerExchange(rows, group, dev)
             self._xargs = _lib.ExchangeArgs(rank=self.peers.rank, world=world,
                                             areas=C.cast(self.peers.c_areas, C.POINTER(C.c_void_p)),
-                                            part_out=self._local.data_ptr(), part_lse=self._local.data_ptr() + 4 * lse_off,
-                                            rows=rows, d=d, out=self.out.data_ptr(), lse=None,
+                                            part_out=None, part_lse=None, rows=rows, d=d, out=None, lse=None,
                                             out_dtype=_dtype_code(self.out.dtype), spin_limit=int(spin_limit))
             self.capturable = True
-            self.exchange = {"kind": "peer stores into mapped exchange areas + flags, merged in the same kernel",
-                             "launches": 1, "bytes_per_rank_per_peer": 4 * (n_out + rows)}
+            self.exchange = {"kind": "rows stored into the peers' mapped exchange areas (value + epoch in every 8 bytes), "
+                                     "local parts merge, exchange and final merge in one kernel",
+                             "launches": 1, "merges_local_parts": True,
+                             "bytes_per_rank_per_peer": rows * (d // 2 + 1) * 16}
         elif exchange == "nccl":
+            self._local = torch.empty(n, dtype=torch.float32, device=dev)
+            self._local_step = DecodeStep(q, k_pack, k_params, v_pack, v_params, None, softmax_scale, "k-channel",
+                                          group_size, num_bits, seqlen_k=seqlen_k, k_res=k_res, v_res=v_res,
+                                          res_lens=res_lens, cache_seqlens=cache_seqlens,
+                                          out=self._local[:n_out].view(b, 1, h, d), lse=self._local[lse_off:lse_off + rows])
             self._gathered = torch.empty(world * n, dtype=torch.float32, device=dev)
             base = self._gathered.data_ptr()
             self._po = (C.c_void_p * world)(*[base + 4 * (r * n) for r in range(world)])
@@ -231,11 +237,12 @@ class SequenceParallelStep:
             raise ValueError("exchange must be 'peer' or 'nccl'")
 
     def step(self):
-        self._local_step.step()
         with torch.cuda.device(self._dev):
             if self.kind == "peer":
-                _lib.check(_lib.load().bd_exchange_combine(C.byref(self._xargs), _stream(self._dev)), "bd_exchange_combine")
+                _lib.check(_lib.load().bd_decode_exchange(self._local_step._ref, C.byref(self._xargs), _stream(self._dev)),
+                           "bd_decode_exchange")
             else:
+                self._local_step.step()
                 self._dist.all_gather_into_tensor(self._gathered, self._local, group=self._group)
                 _lib.check(_lib.load().bd_combine(C.byref(self._args), _stream(self._dev)), "bd_combine")
         return self.out

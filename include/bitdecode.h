@@ -289,21 +289,29 @@ int bd_combine(const bd_combine_args *args, bd_stream_t stream);
  * shared), exports it with bd_peer_export (a 64-byte handle to pass to the other processes by any
  * host-side means) and maps the others' with bd_peer_open.  rows = batch * query heads.
  *
- * Step: after the local decode has written this rank's normalised partial (part_out fp32 (rows, 128),
- * part_lse (rows); bd_decode with out_dtype = BD_FP32 and lse), bd_exchange_combine stores the partial
- * into every peer's area with plain 16-byte stores and sets a per-rank flag there, waits (bounded) for
- * the flags of all peers in its own area, merges the `world` partials and writes `out` (and `lse`): the
- * full result on every rank.  It allocates nothing, synchronises nothing on the host and can be
- * captured in a CUDA graph: the step counter ("epoch") lives in the area.  All ranks must call it the
- * same number of times; the areas hold two steps, so ranks may be up to one step apart.
+ * Step, fused with the decode (the fast path): bd_decode_exchange(decode args, exchange args) runs this
+ * rank's decode over its shard of the tokens with every CTA leaving its part in the workspace, and then
+ * ONE more kernel, a warp per (sequence, query head) row: it merges this rank's parts of the row, stores
+ * the row (128 fp32 values and the log-sum-exp, every 8 bytes carrying the step's epoch beside the
+ * value, so that no fence or separate flag is needed) into every peer's area with plain 16-byte stores,
+ * polls (bounded) for the peers' rows in its own area, merges the `world` partials and writes `out`
+ * (and `lse`) of the decode args: the full result on every rank.  part_out, part_lse, out, lse,
+ * out_dtype of the exchange args are not used; rows must be b * h.
+ * Step, as a call of its own: bd_exchange_combine does the same for a partial that is already there
+ * (part_out fp32 (rows, 128), part_lse (rows), normalised within this rank's tokens; e.g. from bd_decode
+ * with out_dtype = BD_FP32 and lse).
+ * Neither allocates or synchronises on the host, both can be captured in a CUDA graph: the step counter
+ * ("epoch") lives in the area.  All ranks must make the same number of calls on an area; the areas
+ * hold two steps, so ranks may be up to one step apart.
  *
- * A rank whose peer does not publish within `spin_limit` polls (0 = the default, seconds) does not
- * write `out`; its kernel puts BD_ERR_TIMEOUT into the area's status word and returns normally.
+ * A row whose peers do not publish within `spin_limit` polls (0 = the default, seconds) is not written;
+ * the kernel puts BD_ERR_TIMEOUT into the area's status word and returns normally.
  * bd_exchange_state waits for `stream`, returns that word (and clears it) and the area's epoch.
  * After a timeout the ranks are out of step: zero all areas (with the ranks quiesced) before going on.
  *
  * bd_exchange_put publishes a partial into an area from the HOST side (copies + flag), standing in for
- * a peer's kernel: for tests on one GPU and for partials that arrive by other means.  Synchronises.
+ * a peer's kernel (records built on the host, one copy): for tests on one GPU and for partials that
+ * arrive by other means.  Synchronises.
  */
 typedef struct bd_exchange_args {
     int32_t rank, world;                  /* world <= BD_MAX_PARTS */
@@ -326,6 +334,7 @@ int bd_peer_export(const void *ptr, void *handle64);
 int bd_peer_open(const void *handle64, void **ptr);
 int bd_peer_close(void *ptr);
 int bd_exchange_combine(const bd_exchange_args *args, bd_stream_t stream);
+int bd_decode_exchange(const bd_decode_args *decode, const bd_exchange_args *exchange, bd_stream_t stream);
 int bd_exchange_put(void *area, int world, int64_t rows, int from_rank, uint32_t epoch, const float *part_out,
                     const float *part_lse, bd_stream_t stream);
 int bd_exchange_state(const void *area, bd_stream_t stream, uint32_t *epoch_out);

@@ -71,6 +71,63 @@ def test_exchange_merges_what_the_peers_published_over_three_steps():
             lib.bd_peer_free(p)
 
 
+@pytest.mark.parametrize("b,s,gq,ragged", [(1, 8192, 4, False), (3, 2048, 8, True), (2, 768, 1, False)])
+def test_decode_fused_with_the_exchange_equals_the_whole_sequence_on_one_gpu(b, s, gq, ragged):
+    """bd_decode_exchange as rank 0 of two: rank 1's rows (the second half of every sequence, decoded on
+    the same GPU beforehand) are published into rank 0's area from the host side; rank 0's step decodes
+    the first half, merges its CTAs' parts, takes the peer's rows and must give the oracle's result for
+    the whole sequence.  Two steps in a row (both slots of the area)."""
+    import bitladder_b200 as B
+    from bitladder_b200 import _lib
+    from tests import gpu_util as G, helpers as H
+    lib = _lib.load()
+    h_k, bits, group = 2, 4, 128
+    h = h_k * gq
+    x = H.gen_qkv(b, s, h, h_k, seed=31 + b)
+    scale = H.default_scale()
+    half = s // 2
+    seqlens = None
+    if ragged:
+        seqlens = np.array([s, s - 700, half + 1][:b], dtype=np.int32)
+    ref = H.oracle_pack(x["k"], x["v"], bits, group, "fp16")
+    o_ref, _ = H.oracle_decode(x["q"], ref, scale, bits, group, "fp16", cache_seqlens=seqlens)
+    q = x["q"].cuda()
+    lo = G.pack_gpu(B, x["k"][:, :half], x["v"][:, :half], bits, group)
+    hi = G.pack_gpu(B, x["k"][:, half:], x["v"][:, half:], bits, group)
+    kw_lo, kw_hi = {}, {}
+    if ragged:
+        kw_lo = dict(cache_seqlens=torch.from_numpy(np.minimum(seqlens, half)).cuda())
+        kw_hi = dict(cache_seqlens=torch.from_numpy(np.maximum(seqlens - half, 0)).cuda())
+    rows = b * h
+    ptrs = _areas(lib, 2, rows)
+    stream = torch.cuda.current_stream().cuda_stream
+    try:
+        p1, l1 = B.fwd_kvcache_int(q, *hi, None, scale, "k-channel", group, bits, out_dtype=torch.float32,
+                                   return_lse=True, **kw_hi)
+        p1 = p1.reshape(rows, 128).contiguous()
+        l1 = l1.reshape(rows).contiguous()
+        step = B.DecodeStep(q, *lo, None, scale, "k-channel", group, bits, **kw_lo)
+        arr = (C.c_void_p * 2)(*ptrs)
+        xa = _lib.ExchangeArgs(rank=0, world=2, areas=C.cast(arr, C.POINTER(C.c_void_p)), part_out=None, part_lse=None,
+                               rows=rows, d=128, out=None, lse=None, out_dtype=_lib.BD_FP16, spin_limit=0)
+        for epoch in (1, 2):
+            assert lib.bd_exchange_put(ptrs[0], 2, rows, 1, epoch, p1.data_ptr(), l1.data_ptr(), stream) == 0
+            step.out.fill_(float("nan"))
+            assert lib.bd_decode_exchange(step._ref, C.byref(xa), stream) == 0
+            ep = C.c_uint32()
+            assert lib.bd_exchange_state(ptrs[0], stream, C.byref(ep)) == 0 and ep.value == epoch
+            err = np.abs(step.out[:, 0].float().cpu().numpy() - o_ref).max()
+            assert err <= 2e-3, (epoch, err)
+        assert step.status() == 0
+        # wrong row count: refused before anything is launched
+        xa.rows = rows + 1
+        assert lib.bd_decode_exchange(step._ref, C.byref(xa), stream) == _lib.BD_ERR_INVALID
+    finally:
+        torch.cuda.synchronize()
+        for p in ptrs:
+            lib.bd_peer_free(p)
+
+
 def test_a_peer_that_never_publishes_is_a_reported_timeout():
     from bitladder_b200 import _lib
     lib = _lib.load()
