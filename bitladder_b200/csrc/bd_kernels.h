@@ -269,7 +269,7 @@ int fill_exchange_params(const ::bd_exchange_args *a, ExchangeParams &p);
 cudaError_t launch_pack(const PackParams &p, int bits, int group, int dtype, cudaStream_t stream);
 cudaError_t launch_prefix(const PrefixParams &p, cudaStream_t stream);
 cudaError_t launch_advance(const AdvanceParams &p, cudaStream_t stream);
-cudaError_t launch_merge_parts(const DecodeParams &p, cudaStream_t stream);
+cudaError_t launch_merge_parts(const DecodeParams &p, bool early, cudaStream_t stream);
 cudaError_t launch_decode(const DecodeParams &p, const CUtensorMap &kmap, const CUtensorMap &vmap,
                           int bits, int group, cudaStream_t stream);
 // `two`: the variant with half as many warps per CTA and two CTAs per SM (see Cfg in bd_decode.cu)
