@@ -54,6 +54,8 @@ namespace bd {
 // Timing trace for development builds only (-DBD_TRACE): per CTA its SM, start, the time every warp
 // left the streaming loop, and the CTA's end, in nanoseconds of the global timer.
 __device__ unsigned long long g_trace[4096 * 32];
+__device__ unsigned long long g_trace2[4096 * 64];      // per warp: loop entry, after 1, 2, 4 blocks (slots 16 w + k)
+#define BD_TRACE_WARP(k) do { if (lane == 0 && blockIdx.x < 4096 && warp < 16) g_trace2[blockIdx.x * 64 + 4 * warp + (k)] = trace_now(); } while (0)
 __device__ __forceinline__ unsigned long long trace_now() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -68,6 +70,7 @@ __device__ __forceinline__ unsigned trace_smid() {
 #endif
 
 #ifndef BD_TRACE
+#define BD_TRACE_WARP(k) do { } while (0)
 #define BD_TRACE_MARK(slot) do { } while (0)
 #endif
 
@@ -631,6 +634,10 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 
         for (int blk = blk0; blk < blk1 && !aborted; ++blk) {
             if (phase == 0 && blk == blk0) { BD_TRACE_MARK(21); }
+            if (blk == blk0) { BD_TRACE_WARP(0); }
+            if (blk == blk0 + 1) { BD_TRACE_WARP(1); }
+            if (blk == blk0 + 2) { BD_TRACE_WARP(2); }
+            if (blk == blk0 + 5) { BD_TRACE_WARP(3); }
             int seqlen_blk = seqlen;              // tokens of the sequence this block may use
             if (p.block_table != nullptr) {
                 int pib = ib, pblk = blk;
@@ -1353,6 +1360,9 @@ __global__ void __launch_bounds__(128, 1) bd_merge_parts_kernel(const DecodePara
 #ifdef BD_TRACE
 extern "C" int bd_trace_read(void *dst, size_t bytes) {
     return int(cudaMemcpyFromSymbol(dst, g_trace, bytes < sizeof(g_trace) ? bytes : sizeof(g_trace)));
+}
+extern "C" int bd_trace2_read(void *dst, size_t bytes) {
+    return int(cudaMemcpyFromSymbol(dst, g_trace2, bytes < sizeof(g_trace2) ? bytes : sizeof(g_trace2)));
 }
 #endif
 

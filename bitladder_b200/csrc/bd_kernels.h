@@ -63,7 +63,7 @@ struct AdvanceParams {
 // writes the defined result for it.  The merge walks the same arithmetic to find
 // the parts.
 // ---------------------------------------------------------------------------
-constexpr int kTailChunk = 64;    // tokens of the unquantized tail per unit
+constexpr int kTailChunk = 32;    // tokens of the unquantized tail per unit (two 16-token steps: about the time of a pack block)
 constexpr int kTailMax = 256;     // longest unquantized tail the kernel accepts
 
 // Units of one sequence: pack blocks of `len` cached tokens (clamped to the capacity s),

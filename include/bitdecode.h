@@ -241,7 +241,7 @@ int bd_plan_splits(int b, int h_k, int64_t max_s, int bits, int sm_count, int ct
 /*
  * Host-side view of that partition, for tests and debugging (pure integer
  * arithmetic, no device work, no counterpart in the reference).  A unit is one
- * pack block or one 64-token chunk of the unquantized tail; a sequence's units are
+ * pack block or one 32-token chunk of the unquantized tail; a sequence's units are
  * its blocks, then its tail chunks.  `table` is null for equal lengths (then every
  * sequence has n_uniform units) or points to HOST memory holding (first unit, unit
  * count) per sequence followed by (total, 0).  bd_partition_segments writes up to
