@@ -54,23 +54,29 @@ __device__ __forceinline__ uint32_t pair_max(uint32_t a, uint32_t b) {
 template <bool BF16> constexpr uint32_t kPairPosInf = BF16 ? 0x7f807f80u : 0x7c007c00u;
 template <bool BF16> constexpr uint32_t kPairNegInf = BF16 ? 0xff80ff80u : 0xfc00fc00u;
 
-// roundf(v) for v = (x - mn) * scale_inv, left in the mantissa of a float: one add.
-//   v lies in [0, maxv + 1e-6] (x >= mn, and (mx - mn) * fl(maxv / (mx - mn)) exceeds maxv by a few
-//   ulps at most), or is NaN (NaN or infinite inputs), which fmaxf turns into 0 exactly like the
-//   reference's fminf(fmaxf(roundf(v), 0), maxv); the clamp from above never acts.
-//   2^22 + 0.5 has an ulp of 0.5, so v + (2^22 + 0.5) rounded toward zero is 2^22 plus
-//   v + 0.5 cut to a multiple of 0.5; cutting the half away too gives floor(v + 0.5), which for
-//   v >= 0 is roundf(v) (ties away from zero).  The integer sits in mantissa bits 1 and up.
-__device__ __forceinline__ uint32_t quant_bits(float x, float mn, float scale_inv) {
-    const float v = fmaxf(__fmul_rn(__fsub_rn(x, mn), scale_inv), 0.0f);
-    return __float_as_uint(__fadd_rz(v, 4194304.5f));
-}
-// acc |= code << (BITS * J), the code taken from quant_bits (one shift, one three-input logic op)
+// Code of x as a bit field, in four instructions (subtract, multiply, add, logic op).
+//   v = (x - mn) * scale_inv lies in [0, maxv + 1e-6] (x >= mn, and (mx - mn) * fl(maxv / (mx - mn))
+//   exceeds maxv by a few ulps at most), or is NaN (NaN or infinite inputs), which the reference's
+//   fminf(fmaxf(roundf(v), 0), maxv) turns into 0; its clamp from above never acts.
+//   * The multiply is by scale_inv / 2^BITS (a power of two: the product is v / 2^BITS, rounded exactly
+//     as v is) with saturation to [0, 1], which also turns NaN into 0: t = v / 2^BITS in [0, 1).
+//   * t + (2^m + 2^-(BITS+1)), rounded toward zero, leaves floor(v + 0.5) = roundf(v) (v >= 0, ties
+//     away from zero) in the mantissa at bit 23 - m - BITS and up: the ulp of the sum is 2^(m-23), the
+//     half is representable beside 2^m for m <= 22 - BITS, and cutting first to that ulp and then to
+//     the integer is one floor.  m is chosen per field so that the code lands where the field sits in
+//     the 16-bit word (field 0 one bit higher, shifted down afterwards).
 template <int BITS, int J>
-__device__ __forceinline__ uint32_t put_field(uint32_t acc, uint32_t qbits) {
+__device__ __forceinline__ uint32_t put_field(uint32_t acc, float x, float mn, float scale_inv_div) {
+    constexpr int kPos = (J == 0) ? 1 : BITS * J;                  // bit where the code lands
+    constexpr int m = 23 - BITS - kPos;
+    static_assert(m >= 0 && m <= 22 - BITS, "magic constant out of range");
+    constexpr float kMagic = float(1u << m) + 1.0f / float(1u << (BITS + 1));
+    float t;
+    asm("mul.rn.sat.f32 %0, %1, %2;" : "=f"(t) : "f"(__fsub_rn(x, mn)), "f"(scale_inv_div));
+    const uint32_t bits = __float_as_uint(__fadd_rz(t, kMagic));
     constexpr uint32_t kMask = ((1u << BITS) - 1u) << (BITS * J);
-    if constexpr (BITS * J == 0) return acc | ((qbits >> 1) & kMask);
-    else return acc | ((qbits << (BITS * J - 1)) & kMask);
+    if constexpr (J == 0) return acc | ((bits >> 1) & kMask);
+    else return acc | (bits & kMask);
 }
 
 // approx_div: divide the way the reference does as it is shipped (built with --use_fast_math,
@@ -196,6 +202,7 @@ bd_pack_kernel(const PackParams p) {
                 mn[gk][e] = a;
                 float sc;
                 scale_from_minmax(a, b, maxv, approx_div, sinv[gk][e], sc);
+                sinv[gk][e] *= 1.0f / float(1 << BITS);      // exact; see put_field
                 mx[gk][e] = sc;   // reuse as the stored scale
             }
         if (T == 0) {
@@ -219,8 +226,8 @@ bd_pack_kernel(const PackParams p) {
                 constexpr int J = decltype(jc)::value;
                 const float2 x = pair_to_float2<BF16>(raw[pi][J]);
                 constexpr int gk = J / FPG;
-                lo = put_field<BITS, J>(lo, quant_bits(x.x, mn[gk][0], sinv[gk][0]));
-                hi = put_field<BITS, J>(hi, quant_bits(x.y, mn[gk][1], sinv[gk][1]));
+                lo = put_field<BITS, J>(lo, x.x, mn[gk][0], sinv[gk][0]);
+                hi = put_field<BITS, J>(hi, x.y, mn[gk][1], sinv[gk][1]);
             };
             put(std::integral_constant<int, 0>{}); put(std::integral_constant<int, 1>{});
             put(std::integral_constant<int, 2>{}); put(std::integral_constant<int, 3>{});
@@ -289,6 +296,7 @@ bd_pack_kernel(const PackParams p) {
                 }
                 float sc;
                 scale_from_minmax(mn[gd], mx[gd], maxv, approx_div, sinv[gd], sc);
+                sinv[gd] *= 1.0f / float(1 << BITS);         // exact; see put_field
                 if (q8 == 0) {
                     vprm[gd][0][t] = __float2half_rn(sc);
                     vprm[gd][1][t] = __float2half_rn(mn[gd]);
@@ -303,8 +311,8 @@ bd_pack_kernel(const PackParams p) {
                     const uint32_t w = r == 0 ? raw[u][J].x : (r == 1 ? raw[u][J].y : (r == 2 ? raw[u][J].z : raw[u][J].w));
                     const float2 x = pair_to_float2<BF16>(w);
                     constexpr int gd = J / FPGV;
-                    lo = put_field<BITS, J>(lo, quant_bits(x.x, mn[gd], sinv[gd]));
-                    hi = put_field<BITS, J>(hi, quant_bits(x.y, mn[gd], sinv[gd]));
+                    lo = put_field<BITS, J>(lo, x.x, mn[gd], sinv[gd]);
+                    hi = put_field<BITS, J>(hi, x.y, mn[gd], sinv[gd]);
                 };
                 put(std::integral_constant<int, 0>{}); put(std::integral_constant<int, 1>{});
                 put(std::integral_constant<int, 2>{}); put(std::integral_constant<int, 3>{});

@@ -35,10 +35,11 @@ def _args(_lib, rank, ptrs, part, lse, out, rows, spin=0):
     return a
 
 
-def test_exchange_merges_what_the_peers_published_over_three_steps():
+@pytest.mark.parametrize("world", [3, 8])
+def test_exchange_merges_what_the_peers_published_over_three_steps(world):
     from bitladder_b200 import _lib
     lib = _lib.load()
-    world, rows = 3, 40
+    rows = 40
     ptrs = _areas(lib, world, rows)
     stream = torch.cuda.current_stream().cuda_stream
     g = torch.Generator(device="cuda").manual_seed(5)
@@ -48,35 +49,29 @@ def test_exchange_merges_what_the_peers_published_over_three_steps():
             lses = [torch.randn(rows, generator=g, device="cuda") * 3 for _ in range(world)]
             lses[1][7] = float("-inf")                              # a rank with no tokens for one row
             want, _ = O.combine_partials([p.cpu().numpy() for p in parts], [l.cpu().numpy() for l in lses])
-            # ranks 1 and 2 publish into rank 0's area from the host side; then rank 0's kernel runs
-            for r in (1, 2):
-                assert lib.bd_exchange_put(ptrs[0], world, rows, r, epoch, parts[r].data_ptr(), lses[r].data_ptr(), stream) == 0
-            outs = [torch.full((rows, 128), float("nan"), device="cuda") for _ in range(world)]
-            assert lib.bd_exchange_combine(C.byref(_args(_lib, 0, ptrs, parts[0], lses[0], outs[0], rows)), stream) == 0
-            ep = C.c_uint32()
-            assert lib.bd_exchange_state(ptrs[0], stream, C.byref(ep)) == 0 and ep.value == epoch
-            assert np.abs(outs[0].cpu().numpy() - want).max() <= 1e-5
-            # rank 1 in turn: rank 0's kernel has stored its partial into area 1, rank 2's comes from the host
-            assert lib.bd_exchange_put(ptrs[1], world, rows, 2, epoch, parts[2].data_ptr(), lses[2].data_ptr(), stream) == 0
-            assert lib.bd_exchange_combine(C.byref(_args(_lib, 1, ptrs, parts[1], lses[1], outs[1], rows)), stream) == 0
-            assert lib.bd_exchange_state(ptrs[1], stream, C.byref(ep)) == 0 and ep.value == epoch
-            assert np.abs(outs[1].cpu().numpy() - want).max() <= 1e-5
-            # rank 2: both peers' kernels have published to it
-            assert lib.bd_exchange_combine(C.byref(_args(_lib, 2, ptrs, parts[2], lses[2], outs[2], rows)), stream) == 0
-            assert lib.bd_exchange_state(ptrs[2], stream, C.byref(ep)) == 0 and ep.value == epoch
-            assert np.abs(outs[2].cpu().numpy() - want).max() <= 1e-5
+            # The ranks run one after the other.  When rank k runs, the ranks before it have already stored
+            # their rows into its area (their kernels ran); the ranks after it publish from the host side.
+            for k in range(world):
+                for r in range(k + 1, world):
+                    assert lib.bd_exchange_put(ptrs[k], world, rows, r, epoch, parts[r].data_ptr(), lses[r].data_ptr(), stream) == 0
+                out = torch.full((rows, 128), float("nan"), device="cuda")
+                assert lib.bd_exchange_combine(C.byref(_args(_lib, k, ptrs, parts[k], lses[k], out, rows)), stream) == 0
+                ep = C.c_uint32()
+                assert lib.bd_exchange_state(ptrs[k], stream, C.byref(ep)) == 0 and ep.value == epoch
+                assert np.abs(out.cpu().numpy() - want).max() <= 1e-5, (epoch, k)
     finally:
         torch.cuda.synchronize()
         for p in ptrs:
             lib.bd_peer_free(p)
 
 
-@pytest.mark.parametrize("b,s,gq,ragged", [(1, 8192, 4, False), (3, 2048, 8, True), (2, 768, 1, False)])
-def test_decode_fused_with_the_exchange_equals_the_whole_sequence_on_one_gpu(b, s, gq, ragged):
-    """bd_decode_exchange as rank 0 of two: rank 1's rows (the second half of every sequence, decoded on
-    the same GPU beforehand) are published into rank 0's area from the host side; rank 0's step decodes
-    the first half, merges its CTAs' parts, takes the peer's rows and must give the oracle's result for
-    the whole sequence.  Two steps in a row (both slots of the area)."""
+@pytest.mark.parametrize("b,s,gq,ragged,world", [(1, 8192, 4, False, 2), (3, 2048, 8, True, 2), (2, 768, 1, False, 2),
+                                                 (2, 4096, 4, False, 8), (1, 4096, 2, True, 16), (2, 1536, 4, False, 3)])
+def test_decode_fused_with_the_exchange_equals_the_whole_sequence_on_one_gpu(b, s, gq, ragged, world):
+    """bd_decode_exchange as rank 0 of `world`: the other ranks' rows (their shards of every sequence,
+    decoded on the same GPU beforehand) are published into rank 0's area from the host side; rank 0's step
+    decodes the first shard, merges its CTAs' parts, takes the peers' rows and must give the oracle's
+    result for the whole sequence.  Two steps in a row (both slots of the area)."""
     import bitladder_b200 as B
     from bitladder_b200 import _lib
     from tests import gpu_util as G, helpers as H
@@ -85,33 +80,38 @@ def test_decode_fused_with_the_exchange_equals_the_whole_sequence_on_one_gpu(b, 
     h = h_k * gq
     x = H.gen_qkv(b, s, h, h_k, seed=31 + b)
     scale = H.default_scale()
-    half = s // 2
+    shard = s // world
+    assert shard % 128 == 0
     seqlens = None
     if ragged:
-        seqlens = np.array([s, s - 700, half + 1][:b], dtype=np.int32)
+        seqlens = np.array([s, s - 700, shard + 1][:b], dtype=np.int32)
     ref = H.oracle_pack(x["k"], x["v"], bits, group, "fp16")
     o_ref, _ = H.oracle_decode(x["q"], ref, scale, bits, group, "fp16", cache_seqlens=seqlens)
     q = x["q"].cuda()
-    lo = G.pack_gpu(B, x["k"][:, :half], x["v"][:, :half], bits, group)
-    hi = G.pack_gpu(B, x["k"][:, half:], x["v"][:, half:], bits, group)
-    kw_lo, kw_hi = {}, {}
-    if ragged:
-        kw_lo = dict(cache_seqlens=torch.from_numpy(np.minimum(seqlens, half)).cuda())
-        kw_hi = dict(cache_seqlens=torch.from_numpy(np.maximum(seqlens - half, 0)).cuda())
     rows = b * h
-    ptrs = _areas(lib, 2, rows)
+    ptrs = _areas(lib, world, rows)
     stream = torch.cuda.current_stream().cuda_stream
     try:
-        p1, l1 = B.fwd_kvcache_int(q, *hi, None, scale, "k-channel", group, bits, out_dtype=torch.float32,
-                                   return_lse=True, **kw_hi)
-        p1 = p1.reshape(rows, 128).contiguous()
-        l1 = l1.reshape(rows).contiguous()
-        step = B.DecodeStep(q, *lo, None, scale, "k-channel", group, bits, **kw_lo)
-        arr = (C.c_void_p * 2)(*ptrs)
-        xa = _lib.ExchangeArgs(rank=0, world=2, areas=C.cast(arr, C.POINTER(C.c_void_p)), part_out=None, part_lse=None,
-                               rows=rows, d=128, out=None, lse=None, out_dtype=_lib.BD_FP16, spin_limit=0)
+        peers = []
+        step = None
+        for r in range(world):
+            lo, hi = r * shard, (r + 1) * shard
+            bufs = G.pack_gpu(B, x["k"][:, lo:hi], x["v"][:, lo:hi], bits, group)
+            kw = {}
+            if ragged:
+                kw = dict(cache_seqlens=torch.from_numpy(np.clip(seqlens - lo, 0, shard).astype(np.int32)).cuda())
+            if r == 0:
+                step = B.DecodeStep(q, *bufs, None, scale, "k-channel", group, bits, **kw)
+            else:
+                p, l = B.fwd_kvcache_int(q, *bufs, None, scale, "k-channel", group, bits, out_dtype=torch.float32,
+                                         return_lse=True, **kw)
+                peers.append((p.reshape(rows, 128).contiguous(), l.reshape(rows).contiguous()))
+        arr = (C.c_void_p * world)(*ptrs)
+        xa = _lib.ExchangeArgs(rank=0, world=world, areas=C.cast(arr, C.POINTER(C.c_void_p)), part_out=None,
+                               part_lse=None, rows=rows, d=128, out=None, lse=None, out_dtype=_lib.BD_FP16, spin_limit=0)
         for epoch in (1, 2):
-            assert lib.bd_exchange_put(ptrs[0], 2, rows, 1, epoch, p1.data_ptr(), l1.data_ptr(), stream) == 0
+            for r, (p, l) in enumerate(peers, start=1):
+                assert lib.bd_exchange_put(ptrs[0], world, rows, r, epoch, p.data_ptr(), l.data_ptr(), stream) == 0
             step.out.fill_(float("nan"))
             assert lib.bd_decode_exchange(step._ref, C.byref(xa), stream) == 0
             ep = C.c_uint32()
