@@ -506,10 +506,13 @@ def measure(B, name, w, args, device, rank, world, dist, steps, warmup, want_e2e
                          "are summed over ranks"}
 
     sm = torch.cuda.get_device_properties(device).multi_processor_count
-    rows = args.num_splits * sh.b if args.num_splits > 0 else B.plan_splits(sh.b, sh.h_k, sh.s, w["bits"], sm)
-    fused_exchange = bool(exchange and exchange.get("merges_local_parts"))      # no parts-merge kernel then
-    launches = (1 + (1 if w["ragged"] else 0) + (1 if rows > 4 * sh.b and not fused_exchange else 0) +
-                (exchange["launches"] if exchange else 0))
+    local = runs[0]._local_step if seq_split else runs[0]
+    plan = local.plan()                      # what the library does with these arguments on this device
+    rows = plan["rows"]
+    # the library's own count (prefix table of a ragged batch, decode, parts merge); the exchange of a sequence
+    # split merges the parts itself, so its kernel takes the place of the parts merge
+    fused_exchange = bool(exchange and exchange.get("merges_local_parts"))
+    launches = plan["launches"] - (1 if fused_exchange and rows > 4 * sh.b else 0) + (exchange["launches"] if exchange else 0)
     peak, peak_src = measured_peak_gbs()
     achieved = local_bytes / (ms_per_step * 1e-3) / 1e9        # this rank's bytes over the step time (slowest rank's time)
     ratio = NCU_TRAFFIC_RATIO.get(name if world == 1 else "")
@@ -524,7 +527,7 @@ def measure(B, name, w, args, device, rank, world, dist, steps, warmup, want_e2e
                                         if ratio else None),
                      "peak_source": peak_src, "algorithmic_bytes_per_step": local_bytes,
                      "note": "per GPU: this rank's algorithmic bytes per step / CUDA-event time of the whole step"},
-        "launch": launch, "rows_per_kv_head": rows, "gpu_launches_per_step": launches,
+        "launch": launch, "rows_per_kv_head": rows, "ctas_per_sm": plan["ctas_per_sm"], "gpu_launches_per_step": launches,
         "l2": f"{copies} rotating packed-cache copies of {local_bytes / 2**20:.1f} MiB each per GPU "
               f"({copies * local_bytes / 2**20:.0f} MiB against {L2_BYTES // 2**20} MiB of L2)",
         "per_gpu": {"batch": sh.b, "kv_heads": sh.h_k, "tokens": sh.s},
@@ -697,7 +700,8 @@ def main():
     if rank == 0:
         r = main_res
         cfg = job_config(name, w, world)
-        cfg.update({"per_gpu": r["per_gpu"], "rows_per_kv_head": r["rows_per_kv_head"], "launch": r["launch"], "l2": r["l2"],
+        cfg.update({"per_gpu": r["per_gpu"], "rows_per_kv_head": r["rows_per_kv_head"], "ctas_per_sm": r["ctas_per_sm"],
+                    "launch": r["launch"], "l2": r["l2"],
                     "timed": f"{r['regions']} regions of {steps} steps each, median (p20 {r['us_per_step_p20']:.2f} us, "
                              f"p80 {r['us_per_step_p80']:.2f} us per step)"})
         line = {

@@ -18,7 +18,7 @@ BD_PACK_APPROX_DIV = 1
 BD_ERR_INVALID, BD_ERR_TIMEOUT, BD_ERR_SCRATCH_LIMIT, BD_ERR_PAGE, BD_ERR_CAPACITY = -1, -7, -8, -9, -10
 
 EXPORTS = (
-    "bd_pack", "bd_decode", "bd_decode_workspace_bytes", "bd_plan_splits",
+    "bd_pack", "bd_decode", "bd_decode_workspace_bytes", "bd_plan_splits", "bd_decode_plan",
     "bd_combine", "bd_read_status", "bd_strerror", "bd_version",
     "bd_partition_segments", "bd_partition_parts",
     "bd_decode_noalloc", "bd_noalloc_scratch_bytes",
@@ -121,6 +121,8 @@ def load():
     lib.bd_decode_workspace_bytes.restype = C.c_size_t
     lib.bd_plan_splits.argtypes = [C.c_int, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int]
     lib.bd_plan_splits.restype = C.c_int
+    lib.bd_decode_plan.argtypes = [C.POINTER(DecodeArgs), C.POINTER(C.c_int32)]
+    lib.bd_decode_plan.restype = C.c_int
     lib.bd_combine.argtypes = [C.POINTER(CombineArgs), C.c_void_p]
     lib.bd_combine.restype = C.c_int
     lib.bd_partition_segments.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]

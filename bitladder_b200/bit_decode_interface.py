@@ -418,6 +418,14 @@ class DecodeStep:
                 _check_status(self._workspace, self._device)
         return (self.out, self.lse) if self.lse is not None else self.out
 
+    def plan(self) -> dict:
+        """How the library runs this step on the tensors' device: ranges per KV head (``rows``), CTAs
+        resident per SM, streaming warps per CTA and kernels launched per step."""
+        out = (C.c_int32 * 4)()
+        with torch.cuda.device(self._device):
+            _lib.check(_lib.load().bd_decode_plan(self._ref, out), "bd_decode_plan")
+        return {"rows": int(out[0]), "ctas_per_sm": int(out[1]), "warps_per_cta": int(out[2]), "launches": int(out[3])}
+
     def status(self) -> int:
         """Wait for the stream; return (and clear) the error code the steps so far left: 0 for none."""
         with torch.cuda.device(self._device):

@@ -295,6 +295,23 @@ const char *bd_strerror(int code) {
     }
 }
 
+int bd_decode_plan(const bd_decode_args *a, int32_t out[4]) {
+    if (!out) return BD_ERR_INVALID;
+    int rc = check_decode_args(a);
+    if (rc != BD_OK) return rc;
+    DeviceInfo info;
+    rc = current_device_info(info);
+    if (rc != BD_OK) return rc;
+    DecodePlan plan;
+    make_plan(a, info.sm_count, plan);
+    const int gq = a->h / a->h_k;
+    out[0] = plan.rows;
+    out[1] = bd::decode_ctas_per_sm(a->bits, a->group, gq, plan.two_ctas);
+    out[2] = bd::decode_warps(a->bits, a->group, gq, plan.two_ctas);
+    out[3] = (plan.ragged ? 1 : 0) + 1 + (plan.rows > 4 * a->b ? 1 : 0) + (a->advance ? 2 : 0);
+    return BD_OK;
+}
+
 int bd_plan_splits(int b, int h_k, int64_t max_s, int bits, int sm_count, int ctas_per_sm) {
     if (bits != 2 && bits != 4) return 1;
     return plan_rows(b, h_k, max_s, bits, sm_count, ctas_per_sm);

@@ -239,6 +239,16 @@ size_t bd_noalloc_scratch_bytes(void);
 int bd_plan_splits(int b, int h_k, int64_t max_s, int bits, int sm_count, int ctas_per_sm);
 
 /*
+ * What bd_decode will do with these arguments on the current device: out[0] = rows (ranges per KV
+ * head; the grid is rows * h_k CTAs), out[1] = CTAs resident per SM (2: the variant with two smaller
+ * CTAs, taken where whole rows of KV heads would leave more than a tenth of the SMs without a CTA),
+ * out[2] = streaming warps per CTA, out[3] = kernels launched per call (prefix table of a ragged
+ * batch, decode, parts merge, roll-over).  No counterpart in the reference (its grid is
+ * (1, num_splits, b * h_k), csrc/bit_decode/src/flash_fwd_launch_template.h:110).
+ */
+int bd_decode_plan(const bd_decode_args *args, int32_t out[4]);
+
+/*
  * Host-side view of that partition, for tests and debugging (pure integer
  * arithmetic, no device work, no counterpart in the reference).  A unit is one
  * pack block or one 32-token chunk of the unquantized tail; a sequence's units are

@@ -217,3 +217,25 @@ def test_many_short_ragged_sequences(bits, dtype):
     cs[b - 1], rl[b - 1] = 0, 0    # empty at the very end
     out, lse = _run(B, x, bufs, bits, 128, dtype, k_res=x["k_res"], v_res=x["v_res"], cache_seqlens=cs, res_lens=rl)
     _check(x, ref, out, lse, bits, 128, dtype, cs, rl, res=True)
+
+
+def test_plan_reports_what_the_step_launches():
+    """DecodeStep.plan(): ranges per KV head, CTAs per SM and launches as the library plans them on this GPU."""
+    import bitladder_b200 as B
+    sm = torch.cuda.get_device_properties(0).multi_processor_count
+    q = torch.zeros(8, 1, 32, 128, dtype=torch.float16, device="cuda")
+    bufs = B.alloc_packed_cache(8, 4096, 8, 128, 4, 128, device="cuda")
+    p = B.DecodeStep(q, *bufs, None, 0.1, "k-channel", 128, 4).plan()
+    assert p["ctas_per_sm"] == 1 and p["warps_per_cta"] == 12 and p["rows"] == sm // 8 and p["launches"] == 1
+    # one long sequence: more than four parts per sequence, merged by a second kernel
+    q1 = torch.zeros(1, 1, 32, 128, dtype=torch.float16, device="cuda")
+    bufs1 = B.alloc_packed_cache(1, 32768, 8, 128, 4, 128, device="cuda")
+    p1 = B.DecodeStep(q1, *bufs1, None, 0.1, "k-channel", 128, 4).plan()
+    assert p1["rows"] == sm // 8 and p1["launches"] == 2
+    # 32 KV heads: whole rows of heads leave SMs without a CTA, two smaller CTAs per SM fill them
+    q2 = torch.zeros(32, 1, 32, 128, dtype=torch.float16, device="cuda")
+    bufs2 = B.alloc_packed_cache(32, 16384, 32, 128, 4, 128, device="cuda")       # (needs enough blocks per CTA slot)
+    seqlens = torch.full((32,), 16000, dtype=torch.int32, device="cuda")
+    p2 = B.DecodeStep(q2, *bufs2, None, 0.1, "k-channel", 128, 4, cache_seqlens=seqlens).plan()
+    if sm == 148:
+        assert p2 == {"rows": 9, "ctas_per_sm": 2, "warps_per_cta": 6, "launches": 2}
