@@ -15,7 +15,7 @@ BD_OK = 0
 BD_FP16, BD_BF16, BD_FP32 = 0, 1, 2
 BD_MAX_PARTS = 16
 BD_PACK_APPROX_DIV = 1
-BD_ERR_INVALID, BD_ERR_TIMEOUT, BD_ERR_SCRATCH_LIMIT, BD_ERR_PAGE, BD_ERR_CAPACITY = -1, -7, -8, -9, -10
+BD_ERR_INVALID, BD_ERR_TIMEOUT, BD_ERR_SCRATCH_LIMIT, BD_ERR_PAGE, BD_ERR_CAPACITY, BD_ERR_POSITION = -1, -7, -8, -9, -10, -11
 
 EXPORTS = (
     "bd_pack", "bd_decode", "bd_decode_workspace_bytes", "bd_plan_splits", "bd_decode_plan",
@@ -65,6 +65,9 @@ class DecodeArgs(C.Structure):
         ("block_table", C.c_void_p), ("block_table_stride", C.c_int32), ("num_pages", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("advance", C.c_int32), ("spin_limit", C.c_uint32), ("test_starve", C.c_int32),
+        ("rotary_cos", C.c_void_p), ("rotary_sin", C.c_void_p),
+        ("rotary_dim", C.c_int32), ("rotary_interleaved", C.c_int32), ("rotary_positions", C.c_int32),
+        ("reserved0", C.c_int32),
     ]
 
 

@@ -180,7 +180,7 @@ def kvcache_pack_int(k_cache: torch.Tensor, k_pack: torch.Tensor, k_params: torc
 
 def _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
                  k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, lse, num_splits, block_table=None,
-                 k_new=None, v_new=None, spin_limit=0, test_starve=0, advance=False):
+                 k_new=None, v_new=None, spin_limit=0, test_starve=0, advance=False, rotary=None):
     b, s_cap, h_k, d = _check_packed(k_pack, k_params, v_pack, v_params, num_bits, group_size)
     _require(q.dim() == 4 and q.shape[1] == 1, "q must be (b, 1, h, d): one query token per sequence")
     num_pages = 0
@@ -253,6 +253,18 @@ def _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_siz
         _require(k_res.shape[1] >= pack_block_tokens(num_bits),
                  f"advance needs a tail buffer of at least {pack_block_tokens(num_bits)} rows (one pack block)")
         a.advance = 1
+    if rotary is not None:
+        cos, sin, interleaved = rotary
+        _require(k_new is not None, "rotary embedding applies to the appended token: k_new/v_new are needed")
+        _require(cos.is_cuda and sin.is_cuda and cos.device == q.device and sin.device == q.device,
+                 "rotary_cos / rotary_sin must be CUDA tensors on q's device")
+        _require(cos.dtype == q.dtype and sin.dtype == q.dtype, "rotary_cos / rotary_sin must have q's dtype")
+        _require(cos.dim() == 2 and cos.shape == sin.shape and cos.is_contiguous() and sin.is_contiguous(),
+                 "rotary_cos / rotary_sin must be contiguous (positions, rotary_dim / 2)")
+        rotary_dim = 2 * cos.shape[1]
+        _require(0 < rotary_dim <= d and rotary_dim % 16 == 0, "rotary_dim must be a multiple of 16, at most head_dim")
+        a.rotary_cos, a.rotary_sin = cos.data_ptr(), sin.data_ptr()
+        a.rotary_dim, a.rotary_interleaved, a.rotary_positions = rotary_dim, 1 if interleaved else 0, cos.shape[0]
     return a
 
 
@@ -296,7 +308,9 @@ def fwd_kvcache_int(q: torch.Tensor,
                     out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
                     workspace: Optional[torch.Tensor] = None, num_splits: int = 0,
                     k_new: Optional[torch.Tensor] = None, v_new: Optional[torch.Tensor] = None,
-                    check: bool = False, spin_limit: int = 0, _test_starve: int = 0, advance: bool = False):
+                    check: bool = False, spin_limit: int = 0, _test_starve: int = 0, advance: bool = False,
+                    rotary_cos: Optional[torch.Tensor] = None, rotary_sin: Optional[torch.Tensor] = None,
+                    rotary_interleaved: bool = True):
     """One decode-attention step over the packed cache; returns ``out`` (b, 1, h, d).
 
     Same positional signature as the reference (``bit_decode_interface.py:43-86``),
@@ -317,7 +331,11 @@ def fwd_kvcache_int(q: torch.Tensor,
     instead: after the step ``res_lens`` is one larger, and a tail that has reached one pack block is
     quantize-packed as the sequence's next block, ``cache_seqlens`` grows by that block and ``res_lens``
     starts again at 0 (the roll-over of the reference's residual scheme), so a decoder step needs no host
-    logic and can be captured in a CUDA graph.  Asynchronous on the current stream, unless ``check=True``: then the
+    logic and can be captured in a CUDA graph; ``rotary_cos``/``rotary_sin`` (positions, rotary_dim / 2, q's dtype),
+    with ``k_new``: q and k_new are rotated at the token's position ``cache_seqlens[b] + res_lens[b]`` first (pairs
+    (2i, 2i+1) if ``rotary_interleaved`` else (i, i + rotary_dim/2); the reference's dormant append path,
+    ``decode_api.cpp:303-318``), so the rotated key is what the step attends over and files in the tail.
+    Asynchronous on the current stream, unless ``check=True``: then the
     call waits for the step and raises ``RuntimeError`` if the kernel reported an error (a device-side
     wait on a copy that ran out after ``spin_limit`` polls, 0 = the library's default of seconds; a
     ``opt_block_table`` entry outside the page pool).  Without ``check`` such a step returns
@@ -332,9 +350,11 @@ def fwd_kvcache_int(q: torch.Tensor,
     else:
         _require(out.shape == q.shape and out.stride(-1) == 1, "out must have q's shape and a contiguous last dimension")
     lse = torch.empty((q.shape[0], q.shape[2]), dtype=torch.float32, device=q.device) if return_lse else None
+    _require((rotary_cos is None) == (rotary_sin is None), "rotary_cos and rotary_sin must be given together")
+    rotary = None if rotary_cos is None else (rotary_cos, rotary_sin, rotary_interleaved)
     a = _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
                      k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, lse, num_splits, opt_block_table,
-                     k_new, v_new, spin_limit, _test_starve, advance)
+                     k_new, v_new, spin_limit, _test_starve, advance, rotary)
     with torch.cuda.device(q.device):
         ws = _workspace_for(a, q.device, workspace)
         _lib.check(_lib.load().bd_decode(C.byref(a), _stream(q.device)), "bd_decode")
@@ -369,7 +389,8 @@ class DecodeStep:
     def __init__(self, q, k_pack, k_params, v_pack, v_params, opt_block_table=None, softmax_scale=1.0,
                  quant_mode="k-channel", group_size=128, num_bits=4, *, k_res=None, v_res=None, res_lens=None,
                  cache_seqlens=None, seqlen_k=None, return_lse=False, out=None, out_dtype=None, num_splits=0,
-                 k_new=None, v_new=None, lse=None, spin_limit=0, _test_starve=0, advance=False):
+                 k_new=None, v_new=None, lse=None, spin_limit=0, _test_starve=0, advance=False,
+                 rotary_cos=None, rotary_sin=None, rotary_interleaved=True):
         _check_config(quant_mode, group_size, num_bits)
         _check_cuda(q, k_pack, k_params, v_pack, v_params, k_res, v_res, res_lens, cache_seqlens, out,
                     opt_block_table, k_new, v_new)
@@ -387,9 +408,11 @@ class DecodeStep:
         else:
             self.lse = (torch.empty((q.shape[0], q.shape[2]), dtype=torch.float32, device=q.device)
                         if return_lse else None)
+        _require((rotary_cos is None) == (rotary_sin is None), "rotary_cos and rotary_sin must be given together")
+        rotary = None if rotary_cos is None else (rotary_cos, rotary_sin, rotary_interleaved)
         self._args = _decode_args(q, k_pack, k_params, v_pack, v_params, softmax_scale, group_size, num_bits,
                                   k_res, v_res, res_lens, cache_seqlens, seqlen_k, out, self.lse, num_splits,
-                                  opt_block_table, k_new, v_new, spin_limit, _test_starve, advance)
+                                  opt_block_table, k_new, v_new, spin_limit, _test_starve, advance, rotary)
         self._device = q.device
         with torch.cuda.device(q.device):
             need = int(_lib.load().bd_decode_workspace_bytes(C.byref(self._args)))
@@ -397,7 +420,7 @@ class DecodeStep:
             self._workspace = torch.zeros(need, dtype=torch.uint8, device=q.device)
         self._args.workspace, self._args.workspace_bytes = self._workspace.data_ptr(), need
         self._keep = (q, k_pack, k_params, v_pack, v_params, opt_block_table, k_res, v_res, res_lens, cache_seqlens,
-                      k_new, v_new)
+                      k_new, v_new, rotary_cos, rotary_sin)
         self._fn = _lib.load().bd_decode
         self._ref = C.byref(self._args)
 

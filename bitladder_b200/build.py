@@ -16,7 +16,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 BUILD_DIR = os.path.join(_HERE, "build")
 LIB_PATH = os.path.join(_HERE, "libbitdecode.so")
-SOURCES = ["bd_pack.cu", "bd_decode.cu", "bd_combine.cu", "bd_exchange.cu", "bd_api.cu"]
+SOURCES = ["bd_pack.cu", "bd_decode.cu", "bd_combine.cu", "bd_exchange.cu", "bd_rope.cu", "bd_api.cu"]
 HEADERS = ["bd_common.cuh", "bd_kernels.h", os.path.join("..", "..", "include", "bitdecode.h")]
 
 NVCC_FLAGS = [

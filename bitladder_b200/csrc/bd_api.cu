@@ -93,7 +93,7 @@ struct DecodePlan {
     int two_ctas;             // two smaller CTAs per SM instead of one (fills the machine better with many KV heads)
     bool ragged;
     int32_t n_uniform;        // units per sequence when the batch is not ragged
-    size_t off_counters, off_table, off_part_out, off_part_lse, off_warp_acc, total_bytes;
+    size_t off_counters, off_table, off_part_out, off_part_lse, off_warp_acc, off_rope_q, off_rope_k, off_rope_v, total_bytes;
 };
 
 inline size_t align16(size_t x) { return (x + 15) & ~size_t(15); }
@@ -153,6 +153,14 @@ int make_plan(const bd_decode_args *a, int sm_count, DecodePlan &plan) {
     plan.off_part_lse = off; off = align16(off + slots * gq * sizeof(float));
     plan.off_warp_acc = off;
     off = align16(off + size_t(a->b) * a->h_k * bd::decode_deposit_floats(a->bits, a->group, gq, plan.two_ctas) * sizeof(float));
+    plan.off_rope_q = plan.off_rope_k = plan.off_rope_v = off;
+    if (a->rotary_dim > 0) {          // rotated copies of q and k_new, and v_new beside them (fp16 / bf16)
+        off = align16(off + size_t(a->b) * a->h * 128 * 2);
+        plan.off_rope_k = off;
+        off = align16(off + size_t(a->b) * a->h_k * 128 * 2);
+        plan.off_rope_v = off;
+        off = align16(off + size_t(a->b) * a->h_k * 128 * 2);
+    }
     plan.total_bytes = off;
     return BD_OK;
 }
@@ -179,6 +187,10 @@ int check_decode_args(const bd_decode_args *a) {
     if (a->k_new && (!aligned16(a->k_new) || !aligned16(a->v_new) || a->new_stride_b % 8 || a->new_stride_h % 8))
         return BD_ERR_ALIGNMENT;
     if (a->k_res && (a->res_len < 0 || a->res_len > 256)) return BD_ERR_UNSUPPORTED;
+    if (a->rotary_dim != 0) {      // rotary embedding of the appended token
+        if (a->rotary_dim < 0 || a->rotary_dim > 128 || a->rotary_dim % 16) return BD_ERR_UNSUPPORTED;
+        if (!a->k_new || !a->rotary_cos || !a->rotary_sin || a->rotary_positions <= 0) return BD_ERR_INVALID;
+    }
     if (a->advance) {      // device-side bookkeeping: appends, ragged lengths, a tail that holds a pack block, no pages
         if (!a->k_new || !a->cache_seqlens || !a->res_lens || a->block_table) return BD_ERR_INVALID;
         if (a->res_len < pack_block_tokens(a->bits) || a->b > 65535) return BD_ERR_INVALID;
@@ -288,6 +300,7 @@ const char *bd_strerror(int code) {
         case BD_ERR_DEVICE: return "device is not compute capability 10.x";
         case BD_ERR_TIMEOUT: return "a bounded wait inside a kernel ran out";
         case BD_ERR_CAPACITY: return "a tail filled up but the packed buffers have no room for another block";
+        case BD_ERR_POSITION: return "a token position lies beyond the rotary tables";
         case BD_ERR_PAGE: return "a block_table entry lies outside [0, num_pages); its tokens were left out";
         case BD_ERR_SCRATCH_LIMIT: return "this call needs more scratch than the library's fixed area holds "
                                           "(bd_noalloc_scratch_bytes); use bd_decode with a workspace";
@@ -308,7 +321,7 @@ int bd_decode_plan(const bd_decode_args *a, int32_t out[4]) {
     out[0] = plan.rows;
     out[1] = bd::decode_ctas_per_sm(a->bits, a->group, gq, plan.two_ctas);
     out[2] = bd::decode_warps(a->bits, a->group, gq, plan.two_ctas);
-    out[3] = (plan.ragged ? 1 : 0) + 1 + (plan.rows > 4 * a->b ? 1 : 0) + (a->advance ? 2 : 0);
+    out[3] = (plan.ragged ? 1 : 0) + (a->rotary_dim > 0 ? 1 : 0) + 1 + (plan.rows > 4 * a->b ? 1 : 0) + (a->advance ? 2 : 0);
     return BD_OK;
 }
 
@@ -469,6 +482,26 @@ static int decode_step(const bd_decode_args *a, const bd_exchange_args *x, bd_st
     // More than four parts per sequence on average (few long sequences cut over all SMs): one warp
     // merging them at the end of the decode kernel would be the tail of the step; a second kernel
     // with a warp per (sequence, query head) does it in parallel.
+    if (a->rotary_dim > 0) {
+        // q and the new key rotated at the token's position into scratch copies; the decode kernel reads those
+        bd::RopeParams rp;
+        std::memset(&rp, 0, sizeof(rp));
+        rp.q = a->q; rp.k_new = a->k_new; rp.v_new = a->v_new;
+        rp.q_stride_b = a->q_stride_b; rp.q_stride_h = a->q_stride_h;
+        rp.new_stride_b = a->new_stride_b; rp.new_stride_h = a->new_stride_h;
+        rp.q_out = ws + plan.off_rope_q; rp.k_out = ws + plan.off_rope_k; rp.v_out = ws + plan.off_rope_v;
+        rp.cos_tab = a->rotary_cos; rp.sin_tab = a->rotary_sin;
+        rp.cache_seqlens = a->cache_seqlens; rp.res_lens = a->res_lens;
+        rp.s = a->s; rp.res_len = a->res_len;
+        rp.b = a->b; rp.h = a->h; rp.h_k = a->h_k;
+        rp.rotary_dim = a->rotary_dim; rp.interleaved = a->rotary_interleaved ? 1 : 0;
+        rp.positions = a->rotary_positions; rp.dtype = a->dtype;
+        rp.status = reinterpret_cast<int32_t *>(ws);
+        err = bd::launch_rope(rp, stream);
+        if (err != cudaSuccess) return BD_ERR_CUDA;
+        p.q = rp.q_out; p.q_stride_b = int64_t(a->h) * 128; p.q_stride_h = 128;
+        p.k_new = rp.k_out; p.v_new = rp.v_out; p.new_stride_b = int64_t(a->h_k) * 128; p.new_stride_h = 128;
+    }
     p.defer_merge = (x || plan.rows > 4 * a->b) ? 1 : 0;
     p.leave_parts = x ? 1 : 0;
     p.two_ctas = plan.two_ctas;

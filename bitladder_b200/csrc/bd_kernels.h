@@ -246,6 +246,22 @@ struct CombinePartsParams {
     int32_t out_dtype;
 };
 
+// Rotary embedding of the step's token (bd_rope.cu): q and k_new rotated at the token's position into
+// scratch copies (b, h, 128) and (b, h_k, 128) that the decode kernel then reads instead (v_new is copied
+// beside them as it is: the decode kernel takes one pair of strides for both new rows).
+struct RopeParams {
+    const void *q, *k_new, *v_new;
+    int64_t q_stride_b, q_stride_h, new_stride_b, new_stride_h;
+    void *q_out, *k_out, *v_out;      // contiguous
+    const void *cos_tab, *sin_tab;    // (positions, rotary_dim / 2), q's dtype
+    const int32_t *cache_seqlens, *res_lens;
+    int32_t s, res_len;               // lengths of every sequence when the arrays are null
+    int32_t b, h, h_k;
+    int32_t rotary_dim, interleaved, positions, dtype;
+    int32_t *status;
+};
+cudaError_t launch_rope(const RopeParams &p, cudaStream_t stream);
+
 // Exchange of a sequence split's partials between GPUs (bd_exchange.cu).
 struct ExchangeParams {
     uint8_t *area[16];               // area of every rank as mapped into this process; area[rank] is local

@@ -40,7 +40,7 @@
 extern "C" {
 #endif
 
-#define BD_VERSION 200
+#define BD_VERSION 201
 
 /* status codes */
 #define BD_OK                0
@@ -52,6 +52,7 @@ extern "C" {
 #define BD_ERR_DEVICE       -6   /* not an sm_100 device */
 #define BD_ERR_TIMEOUT      -7   /* a bounded device-side wait ran out (see bd_read_status) */
 #define BD_ERR_CAPACITY    -10   /* status word: a tail filled up but the packed buffers have no room for its block */
+#define BD_ERR_POSITION    -11   /* status word: a token position beyond the rotary tables (their last row was used) */
 #define BD_ERR_PAGE         -9   /* status word: a block_table entry outside [0, num_pages) was met; its
                                     tokens were left out */
 #define BD_ERR_SCRATCH_LIMIT -8  /* bd_decode_noalloc: the call needs more than the fixed scratch area */
@@ -187,6 +188,21 @@ typedef struct bd_decode_args {
     int32_t test_starve;      /* test hook, leave 0.  1: the warps of the first CTA expect 16 bytes more
                                  than their first copy delivers, so their bounded waits run out (nothing
                                  faults or hangs: the kernel sets BD_ERR_TIMEOUT and returns) */
+    /* Rotary embedding of the step's token (the reference carries this for its append path, dead in its
+     * snapshot: rotary_cos/sin, rotary_dim, is_rotary_interleaved in decode_api.cpp:303-318, 418;
+     * src/include/rotary.h).  With k_new: q and k_new are rotated at the token's position
+     * cache_seqlens[ib] + res_lens[ib] (or s, res_len) before anything else happens, so the step attends
+     * with the rotated query over the rotated new key and files the rotated key in the tail.  cos / sin:
+     * (rotary_positions, rotary_dim / 2) in q's dtype, contiguous.  The first rotary_dim dims of every
+     * head are rotated, in fp32, pairs (2i, 2i+1) when interleaved, else (i, i + rotary_dim/2):
+     * x0' = x0 cos - x1 sin, x1' = x0 sin + x1 cos.  rotary_dim: a multiple of 16, at most d; 0: none.
+     * One small kernel in front of the decode kernel; its rotated copies live in the workspace. */
+    const void *rotary_cos, *rotary_sin;
+    int32_t rotary_dim;
+    int32_t rotary_interleaved;
+    int32_t rotary_positions; /* rows of the tables; a position beyond them uses the last row and sets
+                                 BD_ERR_POSITION in the status word */
+    int32_t reserved0;
 } bd_decode_args;
 
 int bd_decode(const bd_decode_args *args, bd_stream_t stream);
@@ -243,7 +259,7 @@ int bd_plan_splits(int b, int h_k, int64_t max_s, int bits, int sm_count, int ct
  * head; the grid is rows * h_k CTAs), out[1] = CTAs resident per SM (2: the variant with two smaller
  * CTAs, taken where whole rows of KV heads would leave more than a tenth of the SMs without a CTA),
  * out[2] = streaming warps per CTA, out[3] = kernels launched per call (prefix table of a ragged
- * batch, decode, parts merge, roll-over).  No counterpart in the reference (its grid is
+ * batch, rotary embedding, decode, parts merge, roll-over).  No counterpart in the reference (its grid is
  * (1, num_splits, b * h_k), csrc/bit_decode/src/flash_fwd_launch_template.h:110).
  */
 int bd_decode_plan(const bd_decode_args *args, int32_t out[4]);

@@ -401,3 +401,34 @@ def decode_from_packed(q, k_pack, k_params, v_pack, v_params, softmax_scale, bit
     kr = None if k_res is None else to_f32(k_res, dtype)
     vr = None if v_res is None else to_f32(v_res, dtype)
     return decode_attention(qf, kd, vd, softmax_scale, cache_seqlens, kr, vr, res_lens)
+
+
+def apply_rotary(x, cos, sin, positions, interleaved: bool, dtype: str = "fp16"):
+    """Rotary embedding of one token per sequence, the arithmetic of the reference's dormant append path
+    (csrc/bit_decode/src/include/rotary.h:56-63 interleaved pairs, :116-131 pairs half a rotary_dim apart).
+
+    x: (b, heads, d) in `dtype` (fp16 array, or uint16 bf16 bit patterns); cos / sin: (positions, rotary_dim/2)
+    likewise; positions: (b,) row of the tables per sequence.  For a pair (x0, x1):
+        x0' = x0 cos - x1 sin,   x1' = x0 sin + x1 cos
+    in fp32, every product and the sum rounded separately, then rounded once to `dtype`.  Dims from rotary_dim
+    on are copied.  Returns an array like x."""
+    xf = to_f32(x, dtype).copy()
+    cf, sf = to_f32(cos, dtype), to_f32(sin, dtype)
+    half = cf.shape[1]
+    out = xf.copy()
+    for ib in range(xf.shape[0]):
+        c = cf[int(positions[ib])][None, :]
+        s = sf[int(positions[ib])][None, :]
+        if interleaved:
+            x0, x1 = xf[ib, :, 0:2 * half:2], xf[ib, :, 1:2 * half:2]
+        else:
+            x0, x1 = xf[ib, :, :half], xf[ib, :, half:2 * half]
+        y0 = (x0 * c).astype(np.float32) - (x1 * s).astype(np.float32)
+        y1 = (x0 * s).astype(np.float32) + (x1 * c).astype(np.float32)
+        if interleaved:
+            out[ib, :, 0:2 * half:2], out[ib, :, 1:2 * half:2] = y0, y1
+        else:
+            out[ib, :, :half], out[ib, :, half:2 * half] = y0, y1
+    if dtype == "bf16":
+        return f32_to_bf16_bits(out)
+    return out.astype(np.float16)

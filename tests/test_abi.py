@@ -30,8 +30,8 @@ def test_header_symbols_are_exported():
 
 def test_version_and_error_strings():
     lib = _lib.load()
-    assert lib.bd_version() >= 200
-    for code in range(0, -11, -1):
+    assert lib.bd_version() >= 201
+    for code in range(0, -12, -1):
         assert len(_lib.strerror(code)) > 1
     assert "unknown" in _lib.strerror(-99)
 
@@ -40,9 +40,9 @@ def test_struct_sizes_match_the_header_layout():
     # pointers and int64 first, then int32 fields: no padding surprises between ctypes and the C structs
     assert C.sizeof(_lib.PackArgs) == 2 * 8 + 6 * 8 + 4 * 8 + 6 * 8 + 9 * 4 + 4      # nine int32 fields, padded to 8
     assert C.sizeof(_lib.DecodeArgs) % 8 == 0
-    assert _lib.DecodeArgs.workspace_bytes.offset == C.sizeof(_lib.DecodeArgs) - 24
-    assert _lib.DecodeArgs.advance.offset == C.sizeof(_lib.DecodeArgs) - 16        # three int32 and padding behind
-    assert _lib.DecodeArgs.test_starve.offset == C.sizeof(_lib.DecodeArgs) - 8
+    assert _lib.DecodeArgs.workspace_bytes.offset == C.sizeof(_lib.DecodeArgs) - 56
+    assert _lib.DecodeArgs.advance.offset == C.sizeof(_lib.DecodeArgs) - 48        # three int32 and padding, then the rotary fields
+    assert _lib.DecodeArgs.test_starve.offset == C.sizeof(_lib.DecodeArgs) - 40
 
 
 def test_argument_validation_needs_no_device():
