@@ -79,3 +79,48 @@ def test_a_position_beyond_the_tables_is_reported():
     kw.pop("k_new"); kw.pop("v_new")
     with pytest.raises(RuntimeError):
         B.fwd_kvcache_int(x["q"].cuda(), *bufs, None, 0.1, "k-channel", 128, 4, **kw)
+
+
+def test_positions_follow_the_device_side_lengths_in_a_captured_decoder_loop():
+    """A decoder step with rotary captured once as a CUDA graph and replayed: the position of every new token
+    comes from the lengths the device itself advances, across a roll-over of the tail."""
+    from bitladder_b200.kv_cache import PackedKVCache
+    b, h, h_k, bits, group, steps = 2, 4, 1, 4, 128, 40
+    prompt = [100, 250]
+    x = H.gen_qkv(b, 512, h, h_k, seed=81)
+    cache = PackedKVCache(b, 1024, h_k, 128, bits, group, dtype=torch.float16, device="cuda")
+    cache.prefill(x["k"][:, :256].cuda(), x["v"][:, :256].cuda(), seqlens=prompt)
+    cos, sin = _tables(2048, 64, torch.float16, 5)
+    q = torch.zeros(b, 1, h, 128, dtype=torch.float16, device="cuda")
+    kn = torch.zeros(b, 1, h_k, 128, dtype=torch.float16, device="cuda")
+    vn = torch.zeros_like(kn)
+    step = cache.decoder_step(q, kn, vn, 0.1, rotary_cos=cos.cuda(), rotary_sin=sin.cuda(), rotary_interleaved=False)
+    step.step()                                    # warm-up outside the capture, with zero rows: token 0
+    torch.cuda.synchronize()
+    gr = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side), torch.cuda.graph(gr, stream=side):
+        step.step()
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.Generator().manual_seed(6)
+    news = []
+    for i in range(steps):
+        k_i = torch.randn(b, 1, h_k, 128, generator=g).half()
+        news.append(k_i)
+        kn.copy_(k_i); vn.copy_(k_i); q.copy_(torch.randn(b, 1, h, 128, generator=g).half())
+        gr.replay()
+    assert step.status() == 0
+    cache.note_steps(steps + 1)
+    # sequence 0: 100 prompt tokens (tail 100) + warm-up token + 40 tokens: rolled over at 128, tail now 13 rows;
+    # the last rows of the tail are the rotated tokens at positions 128 .. 140
+    lens = [p + 1 + steps for p in prompt]
+    assert cache.seqlens() == lens
+    for ib in range(b):
+        tail_n = lens[ib] % 128
+        for r in range(max(0, tail_n - 5), tail_n):
+            pos = lens[ib] - tail_n + r
+            i = pos - prompt[ib] - 1                      # index into the replayed tokens
+            want = O.apply_rotary(H.to_np(news[i])[ib:ib + 1, 0], H.to_np(cos), H.to_np(sin), [pos], False)
+            got = cache.k_tail[ib, r].cpu().numpy()
+            assert np.array_equal(got.view(np.uint16), want[0].view(np.uint16)), (ib, r, pos)
