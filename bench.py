@@ -70,7 +70,7 @@ WORKLOADS = {
 }
 # DRAM bytes (read + write) of one decode launch relative to its algorithmic bytes, from ncu captures of these
 # workloads (every block is read once; partials and the tail add the rest)
-NCU_TRAFFIC_RATIO = {"C2": 290_989_312 / 287_440_896, "C3": 86_691_072 / 83_902_464}
+NCU_TRAFFIC_RATIO = {"C2": 291_137_536 / 287_440_896, "C3": 86_691_072 / 83_902_464}
 
 
 def algorithmic_bytes(w, seqlens=None, res_lens=None, b=None, h=None, h_k=None, s=None) -> int:
