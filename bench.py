@@ -70,7 +70,8 @@ WORKLOADS = {
 }
 # DRAM bytes (read + write) of one decode launch relative to its algorithmic bytes, from ncu captures of these
 # workloads (every block is read once; partials and the tail add the rest)
-NCU_TRAFFIC_RATIO = {"C2": 291_137_536 / 287_440_896, "C3": 86_691_072 / 83_902_464}
+NCU_TRAFFIC_RATIO = {"C2": 291_137_536 / 287_440_896, "C3": 86_691_072 / 83_902_464,
+                     "C4": 1_230_654_464 / 1_212_579_840, "C1": 4_556_544 / 4_472_832}
 
 
 def algorithmic_bytes(w, seqlens=None, res_lens=None, b=None, h=None, h_k=None, s=None) -> int:
