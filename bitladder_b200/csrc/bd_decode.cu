@@ -384,7 +384,26 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 
     // ---- prologue: first block of this warp ------------------------------------
     SegWalk walk;                   // this warp's segments, in order
-    walk.init(wpart, wrow);
+    if (wpart.table != nullptr) {
+        // ragged batch: the sequence that holds the first unit of this warp's range, looked for by all lanes
+        // at once (smallest ib with first(ib) + count(ib) > f0 or first(ib) >= f0; one round per 32 sequences)
+        const int64_t Tw = wpart.total();
+        const int64_t f0 = wpart.row_begin(wrow, Tw);
+        int start = wpart.b;
+        for (int base = 0; base < wpart.b; base += 32) {
+            const int i = base + lane;
+            bool ok = false;
+            if (i < wpart.b) {
+                const int2 e = *reinterpret_cast<const int2 *>(wpart.table + 2 * i);
+                ok = int64_t(e.x) + e.y > f0 || int64_t(e.x) >= f0;
+            }
+            const uint32_t m = __ballot_sync(0xffffffffu, ok);
+            if (m != 0) { start = base + __ffs(m) - 1; break; }
+        }
+        walk.init_at(wpart, wrow, Tw, start);
+    } else {
+        walk.init(wpart, wrow);
+    }
     BlockCursor ld;                 // next block to copy into this warp's tiles
     ld.init(walk, p.cache_seqlens, p.s, NB);
     if (ld.valid && lane == 0) {

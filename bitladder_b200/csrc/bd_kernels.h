@@ -120,6 +120,16 @@ struct SegWalk {
         f1 = p.row_begin(int64_t(row) + 1, T);
         ib = find_start();
     }
+    // the same with the first sequence found by the caller (the decode kernel searches a ragged table with
+    // all lanes of the warp at once instead of a binary search of dependent loads)
+    BD_HD void init_at(const Partition &p, int row, int64_t T_, int32_t ib_start) {
+        ptp = &p;
+        c = row;
+        T = T_;
+        f0 = p.row_begin(row, T);
+        f1 = p.row_begin(int64_t(row) + 1, T);
+        ib = ib_start;
+    }
     // smallest ib with first(ib) >= f0 or first(ib) + count(ib) > f0
     BD_HD int32_t find_start() const {
         const Partition &pt = *ptp;
