@@ -7,10 +7,11 @@ Only when ONE long sequence is split along its tokens is there an exchange step:
 each rank attends over its token range and the ranks merge their partial
 ``(out, lse)`` with the log-sum-exp rule of the reference's split combine
 (``csrc/bit_decode/src/flash_fwd_kernel.h:1217-1231, 1280-1298``).  The exchange is
-tiny (``b*h*129*4`` bytes per rank) and latency-bound.  On GPUs it is one kernel per rank
-that stores the partial into the peers' memory, waits for theirs and merges
-(``PeerExchange`` / ``bd_exchange_combine``); the portable form is an all-gather (NCCL,
-or gloo in the CPU tests) followed by the local ``bd_combine`` kernel.
+tiny (about a kilobyte per (sequence, query head) row and rank) and latency-bound.  On GPUs
+it is one kernel per rank behind the decode kernel (``PeerExchange`` / ``bd_decode_exchange``):
+it merges the rank's own parts, stores the rows into the peers' memory (value and step counter
+side by side, so that no fence or flag is needed), polls for theirs and merges; the portable form
+is an all-gather (NCCL, or gloo in the CPU tests) followed by the local ``bd_combine`` kernel.
 
 Nothing here allocates per step beyond the gathered partials; the helpers that
 slice caches are meant for set-up time.
