@@ -218,7 +218,7 @@ def _spacer(device):
     import torch
     key = str(device)
     if key not in _SPACER:
-        _SPACER[key] = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=device)      # 1.5 x the 126 MiB L2
+        _SPACER[key] = torch.zeros(48 * 1024 * 1024, dtype=torch.int32, device=device)       # 192 MiB: 1.5 x the L2
     return _SPACER[key]
 
 
@@ -245,10 +245,11 @@ def build_cache(B, w, sh, device, seed, copy):
             k, v = k.to(tdt)[:, :, sh.h_lo:sh.h_hi], v.to(tdt)[:, :, sh.h_lo:sh.h_hi]
             i = ib - sh.b_lo
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            # a fill larger than the L2 first: the inputs just generated leave the L2 (the pack reads them from
-            # HBM, as in a real prefill), and the GPU is still busy with it while the host queues the event and
-            # the launch, so the interval holds the kernel and not the host's launch latency
-            _spacer(device).fill_(0)
+            # a read of a buffer larger than the L2 first: the inputs just generated leave the L2 (the pack reads
+            # them from HBM, as in a real prefill; a read leaves no dirty lines to write back meanwhile), and the
+            # GPU is still busy with it while the host queues the event and the launch, so the interval holds
+            # the kernel and not the host's launch latency
+            _spacer(device).sum()
             e0.record()
             B.kvcache_pack_int(k, bufs[0][i:i + 1], bufs[1][i:i + 1], v, bufs[2][i:i + 1], bufs[3][i:i + 1],
                                None, None, n, "k-channel", w["group"], w["bits"], dst_token_offset=t0 - sh.t_lo)
