@@ -334,7 +334,7 @@ def fwd_kvcache_int(q: torch.Tensor,
     logic and can be captured in a CUDA graph; ``rotary_cos``/``rotary_sin`` (positions, rotary_dim / 2, q's dtype),
     with ``k_new``: q and k_new are rotated at the token's position ``cache_seqlens[b] + res_lens[b]`` first (pairs
     (2i, 2i+1) if ``rotary_interleaved`` else (i, i + rotary_dim/2); the reference's dormant append path,
-    ``decode_api.cpp:303-318``), so the rotated key is what the step attends over and files in the tail.
+    ``decode_api.cpp:316, 418``, ``src/include/flash.h:149-151``), so the rotated key is what the step attends over and files in the tail.
     Asynchronous on the current stream, unless ``check=True``: then the
     call waits for the step and raises ``RuntimeError`` if the kernel reported an error (a device-side
     wait on a copy that ran out after ``spin_limit`` polls, 0 = the library's default of seconds; a

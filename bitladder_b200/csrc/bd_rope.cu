@@ -1,7 +1,7 @@
 // Rotary position embedding of the token a decoder step appends: the query rows and the new key rows of
 // every sequence are rotated at the token's position before the decode kernel attends with them and files
 // the key in the tail.  The reference carries this for its append path (rotary_cos / rotary_sin, rotary_dim,
-// is_rotary_interleaved: csrc/bit_decode/decode_api.cpp:303-318; the arithmetic of
+// is_rotary_interleaved: csrc/bit_decode/src/include/flash.h:121, 149-151, 189 and decode_api.cpp:316; the arithmetic of
 // csrc/bit_decode/src/include/rotary.h:56-63 for interleaved pairs and :116-131 for pairs half a rotary_dim
 // apart), switched off in its snapshot (rotary_dim = 0, decode_api.cpp:418).
 //

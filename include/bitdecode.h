@@ -189,7 +189,8 @@ typedef struct bd_decode_args {
                                  than their first copy delivers, so their bounded waits run out (nothing
                                  faults or hangs: the kernel sets BD_ERR_TIMEOUT and returns) */
     /* Rotary embedding of the step's token (the reference carries this for its append path, dead in its
-     * snapshot: rotary_cos/sin, rotary_dim, is_rotary_interleaved in decode_api.cpp:303-318, 418;
+     * snapshot: rotary_cos_ptr / rotary_sin_ptr / rotary_dim in src/include/flash.h:121, 149-151, 189,
+     * is_rotary_interleaved in decode_api.cpp:316, rotary_dim = 0 at decode_api.cpp:418;
      * src/include/rotary.h).  With k_new: q and k_new are rotated at the token's position
      * cache_seqlens[ib] + res_lens[ib] (or s, res_len) before anything else happens, so the step attends
      * with the rotated query over the rotated new key and files the rotated key in the tail.  cos / sin:

@@ -1,5 +1,5 @@
 """GPU: rotary embedding of the appended token inside the decode step (the reference's dormant append path,
-decode_api.cpp:303-318, rotary.h): the step must attend with the rotated query over the rotated new key and
+decode_api.cpp:316, 418; flash.h:149-151; rotary.h): the step must attend with the rotated query over the rotated new key and
 file exactly the oracle's rotated key in the tail."""
 import math
 
