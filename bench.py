@@ -701,6 +701,7 @@ def main():
                                  "value": r["value"], "hbm_tb_s": r["hbm_tb_s"], "roofline_frac_per_gpu": r["roofline"]["frac"],
                                  "algorithmic_bytes_per_gpu": r["roofline"]["algorithmic_bytes_per_step"],
                                  "per_gpu": r["per_gpu"], "launch": r["launch"], "gpu_launches_per_step": r["gpu_launches_per_step"],
+                                 "rows_per_kv_head": r["rows_per_kv_head"], "ctas_per_sm": r["ctas_per_sm"],
                                  "check": r["check"], "exchange": r["exchange"], "l2": r["l2"]}
             except Exception as exc:                            # noqa: BLE001
                 extras[other] = {"error": str(exc)[:300]}
