@@ -338,6 +338,7 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
         tma_prefetch_desc(&kmap);
         tma_prefetch_desc(&vmap);
     }
+    BD_TRACE_MARK(25);
     // The warps are the rows of the partition with kWarps times the CTA rows.
     Partition wpart = p.part;
     wpart.R = p.part.R * kWarps;
@@ -404,8 +405,10 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
     } else {
         walk.init(wpart, wrow);
     }
+    BD_TRACE_MARK(26);
     BlockCursor ld;                 // next block to copy into this warp's tiles
     ld.init(walk, p.cache_seqlens, p.s, NB);
+    BD_TRACE_MARK(27);
     if (ld.valid && lane == 0) {
         issue_k(ld.sg.ib, ld.u);
         issue_v(ld.sg.ib, ld.u);
