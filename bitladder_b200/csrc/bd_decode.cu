@@ -1324,15 +1324,11 @@ __global__ void __launch_bounds__(128, 1) bd_merge_parts_kernel(const DecodePara
         const bool live = i < nrows && (pr.dense || row_has_part(p.part, ib, pr.c0 + i));
         return live ? __ldcg(p.part_lse + (slot0 + int64_t(i) * p.h_k) * p.gq + qrow) : -INFINITY;
     };
-    // Up to 32 parts at a time: lane i weighs part i, and every lane asks for its 16 bytes of all the
-    // parts of the round before any answer is used (the rows do not depend on the weights), so a
-    // round costs one trip to L2.  Rows of parts that weigh nothing are never used (select, not multiply).
-    const float ls0 = lse_of(lane);
-    float mx = ls0;
-    for (int base = 32; base < nrows; base += 32) mx = fmaxf(mx, lse_of(base + lane));
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-    float sum = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
+    // Up to 32 parts a round: lane i weighs part i, and every lane asks for its 16 bytes of all the parts of
+    // the round together with the round's log-sum-exps before any answer is used (the rows do not depend on
+    // the weights): one trip to L2 per round.  Rows of parts that weigh nothing are never used (select, not
+    // multiply).  A later round brings what was summed so far to the new maximum.
+    float mx = -INFINITY, sum = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
     for (int base = 0; base < nrows; base += 32) {
         const int cnt = min(32, nrows - base);
         float4 v[32];
@@ -1343,7 +1339,14 @@ __global__ void __launch_bounds__(128, 1) bd_merge_parts_kernel(const DecodePara
                 v[j] = __ldcg(reinterpret_cast<const float4 *>(
                     p.part_out + ((slot0 + int64_t(base + j) * p.h_k) * p.gq + qrow) * kHeadDim + 4 * lane));
         }
-        const float ls = base == 0 ? ls0 : lse_of(base + lane);
+        const float ls = lse_of(base + lane);
+        float m2 = ls;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) m2 = fmaxf(m2, __shfl_xor_sync(0xffffffffu, m2, off));
+        m2 = fmaxf(m2, mx);
+        const float fold = (mx == -INFINITY) ? 0.f : __expf(mx - m2);
+        sum *= fold; o[0] *= fold; o[1] *= fold; o[2] *= fold; o[3] *= fold;
+        mx = m2;
         const float w = (ls == -INFINITY || mx == -INFINITY) ? 0.f : __expf(ls - mx);
         float t = w;
 #pragma unroll
@@ -1359,7 +1362,7 @@ __global__ void __launch_bounds__(128, 1) bd_merge_parts_kernel(const DecodePara
         }
     }
     float lse_f = -INFINITY;
-    if (mx != -INFINITY) {
+    if (mx != -INFINITY && sum > 0.f) {
         const float inv = 1.0f / sum;
         o[0] *= inv; o[1] *= inv; o[2] *= inv; o[3] *= inv;
         lse_f = mx + logf(sum);
