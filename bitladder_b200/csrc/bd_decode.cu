@@ -1305,8 +1305,6 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(128, 1) bd_merge_parts_kernel(const DecodeParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // launched early (see launch_merge_parts): everything the decode kernel wrote is visible after this
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t rowid = int64_t(blockIdx.x) * 4 + warp;
     if (rowid >= int64_t(p.b) * p.h) return;
     const int ib = int(rowid / p.h), hq = int(rowid % p.h);
@@ -1324,6 +1322,10 @@ __global__ void __launch_bounds__(128, 1) bd_merge_parts_kernel(const DecodePara
         const bool live = i < nrows && (pr.dense || row_has_part(p.part, ib, pr.c0 + i));
         return live ? __ldcg(p.part_lse + (slot0 + int64_t(i) * p.h_k) * p.gq + qrow) : -INFINITY;
     };
+    // Launched early (see launch_merge_parts), the integer work above ran beside the decode kernel's end (the
+    // partition and a ragged batch's table were final before that kernel started); everything it wrote is
+    // visible after this.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // Up to 32 parts a round: lane i weighs part i, and every lane asks for its 16 bytes of all the parts of
     // the round together with the round's log-sum-exps before any answer is used (the rows do not depend on
     // the weights): one trip to L2 per round.  Rows of parts that weigh nothing are never used (select, not
