@@ -516,7 +516,7 @@ static int decode_step(const bd_decode_args *a, const bd_exchange_args *x, bd_st
         err = bd::launch_exchange_parts(xp, stream);
         if (err != cudaSuccess) return BD_ERR_CUDA;
     } else if (p.defer_merge) {
-        err = bd::launch_merge_parts(p, a->bits == 2, stream);
+        err = bd::launch_merge_parts(p, true, stream);
         if (err != cudaSuccess) return BD_ERR_CUDA;
     }
 
