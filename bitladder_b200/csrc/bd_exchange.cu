@@ -87,17 +87,25 @@ template <bool FROM_PARTS, int MAXW>
 __global__ void __launch_bounds__(kXWarps * 32) bd_exchange_kernel(const ExchangeParams p) {
     uint8_t *mine = p.area[p.rank];
     uint32_t *hdr = reinterpret_cast<uint32_t *>(mine);              // [0] epoch, [1] finished CTAs, [2] status
-    const uint32_t epoch = *reinterpret_cast<volatile uint32_t *>(hdr) + 1;
-    const uint32_t par = epoch & 1u;
+    uint32_t epoch = 0, par = 0;         // read behind the wait: the call before this one may just be moving it on
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     BD_XMARK(0);
 
+    // The kernel is launched early behind the one that produces this rank's partial (programmatic dependent
+    // launch): its set-up runs beside that kernel's end, and what that kernel wrote is read after the wait.
+    bool waited = false;
     for (int64_t row = int64_t(blockIdx.x) * kXWarps + warp; row < p.rows; row += int64_t(gridDim.x) * kXWarps) {
         const int ib = int(row / p.h), hq = int(row % p.h);
         // ---- 1. this rank's partial of the row: lane owns head dims 4 lane .. 4 lane + 3
         float o[4] = {0.f, 0.f, 0.f, 0.f};
         float lse_mine = -INFINITY;
         if constexpr (!FROM_PARTS) {
+            if (!waited) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                epoch = *reinterpret_cast<volatile uint32_t *>(hdr) + 1;
+                par = epoch & 1u;
+                waited = true;
+            }
             const float4 v = *reinterpret_cast<const float4 *>(p.part_out + row * kHeadDim + 4 * lane);
             o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
             lse_mine = p.part_lse[row];
@@ -112,6 +120,12 @@ __global__ void __launch_bounds__(kXWarps * 32) bd_exchange_kernel(const Exchang
                 const bool live = i < nrows && (pr.dense || row_has_part(p.part, ib, pr.c0 + i));
                 return live ? __ldcg(p.part_lse + (slot0 + int64_t(i) * p.h_k) * p.gq + qrow) : -INFINITY;
             };
+            if (!waited) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                epoch = *reinterpret_cast<volatile uint32_t *>(hdr) + 1;
+                par = epoch & 1u;
+                waited = true;
+            }
             // Up to 32 parts a round: lane i weighs part i, and every lane asks for its 16 bytes of all the
             // parts of the round together with the log-sum-exps, before any answer is used: one trip to L2.
             float mx = -INFINITY, sum = 0.f;
@@ -256,12 +270,19 @@ static unsigned xchg_grid(int64_t rows) {
 
 template <bool FROM_PARTS>
 static cudaError_t launch_exchange(const ExchangeParams &p, cudaStream_t stream) {
-    const unsigned grid = xchg_grid(p.rows), threads = kXWarps * 32;
-    if (p.world <= 2) bd_exchange_kernel<FROM_PARTS, 2><<<grid, threads, 0, stream>>>(p);
-    else if (p.world <= 4) bd_exchange_kernel<FROM_PARTS, 4><<<grid, threads, 0, stream>>>(p);
-    else if (p.world <= 8) bd_exchange_kernel<FROM_PARTS, 8><<<grid, threads, 0, stream>>>(p);
-    else bd_exchange_kernel<FROM_PARTS, 16><<<grid, threads, 0, stream>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(xchg_grid(p.rows));
+    cfg.blockDim = dim3(kXWarps * 32);
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;     // staged behind the kernel before it
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    if (p.world <= 2) return cudaLaunchKernelEx(&cfg, bd_exchange_kernel<FROM_PARTS, 2>, p);
+    if (p.world <= 4) return cudaLaunchKernelEx(&cfg, bd_exchange_kernel<FROM_PARTS, 4>, p);
+    if (p.world <= 8) return cudaLaunchKernelEx(&cfg, bd_exchange_kernel<FROM_PARTS, 8>, p);
+    return cudaLaunchKernelEx(&cfg, bd_exchange_kernel<FROM_PARTS, 16>, p);
 }
 cudaError_t launch_exchange_parts(const ExchangeParams &p, cudaStream_t stream) { return launch_exchange<true>(p, stream); }
 static_assert(BD_MAX_PARTS == 16, "the exchange kernel is built for up to 16 ranks");
