@@ -1306,16 +1306,18 @@ bd_decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
 __global__ void __launch_bounds__(128, 1) bd_merge_parts_kernel(const DecodeParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t rowid = int64_t(blockIdx.x) * 4 + warp;
-    if (rowid >= int64_t(p.b) * p.h) return;
+    // (a warp that has nothing to merge still waits for the decode kernel before it leaves: kernels staged behind
+    // this one rely on this kernel not finishing before that one)
+    if (rowid >= int64_t(p.b) * p.h) { asm volatile("griddepcontrol.wait;" ::: "memory"); return; }
     const int ib = int(rowid / p.h), hq = int(rowid % p.h);
     const int ih = hq / p.gq, qrow = hq % p.gq;
     const PartRange pr = part_range(p.part, ib);
     const int nrows = pr.c1 - pr.c0 + 1;
-    if (nrows <= 1) return;
+    if (nrows <= 1) { asm volatile("griddepcontrol.wait;" ::: "memory"); return; }
     if (!pr.dense) {
         int nparts = 0;
         for (int c = pr.c0; c <= pr.c1; ++c) nparts += row_has_part(p.part, ib, c) ? 1 : 0;
-        if (nparts <= 1) return;
+        if (nparts <= 1) { asm volatile("griddepcontrol.wait;" ::: "memory"); return; }
     }
     const int64_t slot0 = (int64_t(pr.c0) + ib) * p.h_k + ih;
     auto lse_of = [&](int i) {
@@ -1494,6 +1496,9 @@ cudaError_t launch_decode(const DecodeParams &p, const CUtensorMap &kmap, const 
 // pack did (a tail that reached one pack block was packed, room permitting).
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) bd_advance_kernel(const AdvanceParams p) {
+    // staged early behind the roll-over pack kernel (which itself waits for the decode kernel): the lengths
+    // may only move when both are done
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int i = blockIdx.x * 256 + threadIdx.x;
     if (i >= p.b) return;
     const int cap = min(kTailMax, p.res_cap);
@@ -1512,8 +1517,16 @@ __global__ void __launch_bounds__(256) bd_advance_kernel(const AdvanceParams p) 
 }
 
 cudaError_t launch_advance(const AdvanceParams &p, cudaStream_t stream) {
-    bd_advance_kernel<<<(p.b + 255) / 256, 256, 0, stream>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned((p.b + 255) / 256));
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;     // staged behind the kernel before it
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, bd_advance_kernel, p);
 }
 
 cudaError_t launch_prefix(const PrefixParams &p, cudaStream_t stream) {

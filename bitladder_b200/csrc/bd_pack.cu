@@ -142,6 +142,11 @@ bd_pack_kernel(const PackParams p) {
     const int ih = blockIdx.x, blk = blockIdx.y, ib = blockIdx.z;
     int dst_off = p.dst_token_offset;
     if (p.roll_res_lens != nullptr) {          // roll-over: only sequences whose tail this step's token filled
+        // The roll-over is staged early behind the decode kernel that files the token, and the kernel that moves
+        // the lengths on is staged behind this one: every CTA waits for the decode kernel before it reads a tail
+        // row or leaves (a CTA that left without waiting would let the lengths move under that kernel).
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         if (p.roll_res_lens[ib] + 1 != NB) return;
         dst_off = p.roll_cache_seqlens[ib];
         if (dst_off < 0 || dst_off % NB != 0 || dst_off + NB > p.roll_s_cap) return;   // no room: reported by the advance kernel
@@ -349,8 +354,16 @@ static cudaError_t launch_pack_t(const PackParams &p, cudaStream_t stream) {
     constexpr int NB = 32 * (16 / BITS);
     constexpr int NTHREADS = kPackThreads;
     dim3 grid(p.h_k, p.s / NB, p.b);
-    bd_pack_kernel<BITS, GROUP, BF16><<<grid, NTHREADS, 0, stream>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = p.roll_res_lens != nullptr ? 1 : 0;           // the roll-over of a decoder step only
+    return cudaLaunchKernelEx(&cfg, bd_pack_kernel<BITS, GROUP, BF16>, p);
 }
 
 cudaError_t launch_pack(const PackParams &p, int bits, int group, int dtype, cudaStream_t stream) {
