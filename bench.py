@@ -292,6 +292,69 @@ def build_inputs(B, w, sh, device, seed, copies):
     return caches, q, extras, seqlens, res_lens, pack_gbs
 
 
+def decoder_step_extra(B, device, seed):
+    """A whole decoder step of the headline shape, captured as one CUDA graph: the decode with the new token
+    attended and filed in the tail, rotary embedding of q and the new key at the token's position, and the
+    device-side bookkeeping (a tail that fills up is quantize-packed as the sequence's next block, the lengths
+    move on).  30 steps per replay from 64-token tails, lengths put back between replays."""
+    import torch
+    from bitladder_b200.kv_cache import PackedKVCache
+    w = WORKLOADS["C2"]
+    b, h, h_k, s, d = w["b"], w["h"], w["h_k"], w["s"], 128
+    g = _gen(device, seed, 31337)
+    caches = []
+    for c in range(3):
+        cache = PackedKVCache(b, s + 1024, h_k, d, w["bits"], w["group"], dtype=torch.float16, device=device)
+        k = torch.randn(1, s + w["res"], h_k, d, generator=g, device=device, dtype=torch.float32).to(torch.float16)
+        v = torch.randn(1, s + w["res"], h_k, d, generator=g, device=device, dtype=torch.float32).to(torch.float16)
+        cache.prefill(k.expand(b, -1, -1, -1).contiguous(), v.expand(b, -1, -1, -1).contiguous())
+        del k, v
+        caches.append(cache)
+    q = torch.randn(b, 1, h, d, generator=g, device=device, dtype=torch.float32).to(torch.float16)
+    kn = torch.randn(b, 1, h_k, d, generator=g, device=device, dtype=torch.float32).to(torch.float16)
+    vn = torch.randn(b, 1, h_k, d, generator=g, device=device, dtype=torch.float32).to(torch.float16)
+    ang = torch.rand(s + 2048, d // 2, generator=g, device=device) * 6.2831853
+    cos, sin = torch.cos(ang).to(torch.float16), torch.sin(ang).to(torch.float16)
+    scale = 1.0 / math.sqrt(d)
+    out = {}
+    for label, kw in (("bookkeeping", {}), ("bookkeeping_and_rotary", dict(rotary_cos=cos, rotary_sin=sin, rotary_interleaved=False))):
+        steps = [c.decoder_step(q, kn, vn, scale, **kw) for c in caches]
+        saved = [(c.cache_seqlens.clone(), c.res_lens.clone()) for c in caches]
+        for st in steps:
+            st.step()
+        torch.cuda.synchronize()
+        per = 30
+        gr, side = torch.cuda.CUDAGraph(), torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.cuda.graph(gr, stream=side):
+            for i in range(per):
+                steps[i % 3].step()
+        torch.cuda.current_stream().wait_stream(side)
+        ts = []
+        for _ in range(12):
+            for c, (a, r) in zip(caches, saved):
+                c.cache_seqlens.copy_(a)
+                c.res_lens.copy_(r)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            gr.replay()
+            e1.record()
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3 / per)
+        out[label] = {"us_per_step": statistics.median(ts), "gpu_launches_per_step": steps[0].plan()["launches"]}
+        rc = steps[0].status()
+        if rc != 0:
+            out[label]["device_status"] = rc
+        for c, (a, r) in zip(caches, saved):
+            c.cache_seqlens.copy_(a)
+            c.res_lens.copy_(r)
+    out["what"] = ("C2 shape with per-sequence lengths: decode + fused append + device-side roll-over and length update "
+                   "(and rotary embedding of q and the new key), one CUDA graph of 30 steps, median of 12 replays")
+    del caches
+    torch.cuda.empty_cache()
+    return out
+
+
 def copies_for(nbytes, asked):
     """Rotating cache copies: at least three, and enough that the set is several times the L2."""
     if asked > 0:
@@ -708,6 +771,13 @@ def main():
                 if world > 1:
                     raise
 
+    decoder_step = None
+    if world == 1 and args.workload is None and not args.no_extras:
+        try:
+            decoder_step = decoder_step_extra(B, device, 1000)
+        except Exception as exc:                                # noqa: BLE001
+            decoder_step = {"error": str(exc)[:300]}
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         sec, cores = cpu_time(w, 1000, 1, steps=10, warmup=1)
@@ -733,6 +803,8 @@ def main():
         }
         if extras:
             line["sharded" if world > 1 else "other_configs"] = extras
+        if decoder_step is not None:
+            line["decoder_step"] = decoder_step
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -189,7 +189,7 @@ int check_decode_args(const bd_decode_args *a) {
     if (a->k_res && (a->res_len < 0 || a->res_len > 256)) return BD_ERR_UNSUPPORTED;
     if (a->rotary_dim != 0) {      // rotary embedding of the appended token
         if (a->rotary_dim < 0 || a->rotary_dim > 128 || a->rotary_dim % 16) return BD_ERR_UNSUPPORTED;
-        if (!a->k_new || !a->rotary_cos || !a->rotary_sin || a->rotary_positions <= 0) return BD_ERR_INVALID;
+        if (!a->k_new || !a->rotary_cos || !a->rotary_sin || a->rotary_positions <= 0 || a->b > 65535) return BD_ERR_INVALID;
     }
     if (a->advance) {      // device-side bookkeeping: appends, ragged lengths, a tail that holds a pack block, no pages
         if (!a->k_new || !a->cache_seqlens || !a->res_lens || a->block_table) return BD_ERR_INVALID;

@@ -8,7 +8,8 @@
 // For a pair (x0, x1) of a head and the table row of the token's position:
 //     x0' = x0 cos - x1 sin,   x1' = x0 sin + x1 cos
 // in fp32 with separately rounded products (no fused multiply-add, so a CPU evaluation gives the same bits),
-// rounded once to the input type.  Dims from rotary_dim on are copied.  One thread per pair.
+// rounded once to the input type.  Dims from rotary_dim on are copied.  One thread per pair, one CTA of 64
+// threads per (sequence, head): every load of the step is in flight at once.
 #include "bd_common.cuh"
 #include "bd_kernels.h"
 
@@ -23,23 +24,23 @@ __device__ __forceinline__ void rope_store(void *p, int64_t i, float v, bool bf1
     else static_cast<__half *>(p)[i] = __float2half_rn(v);
 }
 
-// grid (b), 256 threads: thread t walks the (head, pair) slots of the sequence's q rows, then of its k rows
-__global__ void __launch_bounds__(256) bd_rope_kernel(const RopeParams p) {
-    const int ib = blockIdx.x;
+// grid (q heads + 2 x KV heads, b), 64 threads: thread t is pair t of one head's row: a q head, then a k head
+// (both rotated), then a v head (copied beside them)
+__global__ void __launch_bounds__(64) bd_rope_kernel(const RopeParams p) {
+    const int ib = blockIdx.y;
     const bool bf16 = p.dtype == BD_BF16;
     const int cached = p.cache_seqlens ? max(p.cache_seqlens[ib], 0) : p.s;
     const int tail = p.res_lens ? max(p.res_lens[ib], 0) : p.res_len;
     int pos = cached + tail;
     if (pos >= p.positions) {
-        if (threadIdx.x == 0) atomicExch(p.status, BD_ERR_POSITION);
+        if (threadIdx.x == 0 && blockIdx.x == 0) atomicExch(p.status, BD_ERR_POSITION);
         pos = p.positions - 1;
     }
     const int half = p.rotary_dim / 2;
     constexpr int kPairs = kHeadDim / 2;
-    const int total = (p.h + 2 * p.h_k) * kPairs;          // q heads, k heads (rotated), v heads (copied)
-    for (int i = threadIdx.x; i < total; i += blockDim.x) {
-        const int head = i / kPairs;
-        int pr = i % kPairs;
+    {
+        const int head = blockIdx.x;
+        int pr = threadIdx.x;
         const bool is_q = head < p.h, is_v = head >= p.h + p.h_k;
         const void *src = is_q ? p.q : (is_v ? p.v_new : p.k_new);
         void *dst = is_q ? p.q_out : (is_v ? p.v_out : p.k_out);
@@ -73,7 +74,8 @@ __global__ void __launch_bounds__(256) bd_rope_kernel(const RopeParams p) {
 }
 
 cudaError_t launch_rope(const RopeParams &p, cudaStream_t stream) {
-    bd_rope_kernel<<<unsigned(p.b), 256, 0, stream>>>(p);
+    static_assert(kHeadDim / 2 == 64, "one thread per pair of a 128-dim head");
+    bd_rope_kernel<<<dim3(unsigned(p.h + 2 * p.h_k), unsigned(p.b)), 64, 0, stream>>>(p);
     return cudaGetLastError();
 }
 
