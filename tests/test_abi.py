@@ -77,8 +77,8 @@ def test_plan_splits_fills_the_machine():
     assert plan(8, 8, 32768) == 55                    # 55 rows x 8 heads = 440 CTAs <= 444 resident
     assert plan(32, 32, 16384) == 13
     assert plan(16, 1, 131072) == 444
-    assert plan(1, 8, 4096) == 4                      # small problem: four ranges per sequence
-    assert plan(2, 8, 4096) == 8
+    assert plan(1, 8, 4096) == 16                     # small problem: two blocks per range
+    assert plan(2, 8, 4096) == 32
     assert plan(8, 8, 32768, c=0) == 18               # the kernel's own residency: one CTA per SM
     assert plan(1, 8, 128) == 1
     assert plan(1, 1024, 4096) == 1                   # more heads than slots: one row
